@@ -3,6 +3,7 @@ description that the rest of the package reads."""
 
 from .qwen3 import Qwen3Config
 from .registry import architectures, config_class, read_config, register_architecture
+from .ninenex import NinenexConfig
 from .tifapel import TifapelConfig
 from .voserax import VoseraxConfig
 from .spec import BlockSpec, LayerCall, ModelSpec, PartSpec, TensorSpec, default_schedule
@@ -10,8 +11,9 @@ from .spec import BlockSpec, LayerCall, ModelSpec, PartSpec, TensorSpec, default
 register_architecture("Qwen3ForCausalLM", Qwen3Config)
 register_architecture("Tifapel", TifapelConfig)
 register_architecture("Voserax", VoseraxConfig)
+register_architecture("Ninenex", NinenexConfig)
 
 __all__ = [
-    "Qwen3Config", "TifapelConfig", "VoseraxConfig", "architectures", "config_class", "read_config", "register_architecture",
+    "Qwen3Config", "NinenexConfig", "TifapelConfig", "VoseraxConfig", "architectures", "config_class", "read_config", "register_architecture",
     "BlockSpec", "LayerCall", "ModelSpec", "PartSpec", "TensorSpec", "default_schedule",
 ]

@@ -12,6 +12,8 @@
 // size Dv of their own; a query row may sit in a wider row (q_stride elements
 // from token to token), e.g. the q|k|v row of a fused product.  With `sink` > 0
 // the softmax's denominator has that much added: w_j = exp(s_j) / (sink + sum exp(s_j)).
+// With `chunk` > 0 positions are cut into chunks of that many, counted from the sequence's position 0, and a
+// query sees only the keys of its own chunk: first = p - p % chunk (beside a window, the later of the two).
 //
 // One warp per (token, head).  Keys are taken 32 at a time starting at the
 // range's first key: lane j scores key lo + c*32 + j with a sequential dot over
@@ -30,7 +32,7 @@ __global__ void attention_paged_kernel(const TA* __restrict__ q, TA* __restrict_
                                        const int* __restrict__ block_table, int table_width,
                                        const int* __restrict__ token_seq, const int* __restrict__ token_pos,
                                        int H, int G, int D, int Dv, size_t q_stride, int window, int keep_first,
-                                       float scale, float sink) {
+                                       float scale, float sink, int chunk) {
   extern __shared__ float q_buf[];  // [ATT_WARPS][D]
   pdl_launch_dependents();
   pdl_wait();
@@ -40,7 +42,8 @@ __global__ void attention_paged_kernel(const TA* __restrict__ q, TA* __restrict_
   if (hq >= H) return;
   const int g = hq / (H / G);
   const int p = token_pos[t];
-  const int first = (window > 0 && p - (window - 1) > 0) ? p - (window - 1) : 0;
+  int first = (window > 0 && p - (window - 1) > 0) ? p - (window - 1) : 0;
+  if (chunk > 0) first = max(first, p - p % chunk);
   const int* pages = block_table + (size_t)token_seq[t] * table_width;
 
   float* qs = q_buf + warp * D;
@@ -98,12 +101,13 @@ __global__ void attention_paged_kernel(const TA* __restrict__ q, TA* __restrict_
   }
 }
 
-LLMX_API int llmx_attention_paged(const void* q, void* out, int act_dtype, const void* k_cache,
+LLMX_API int llmx_attention_paged_chunked(const void* q, void* out, int act_dtype, const void* k_cache,
                                   const void* v_cache, int cache_dtype, const int* block_table, int table_width,
                                   const int* token_seq, const int* token_pos, int n_tokens, int H, int G, int D,
                                   int Dv, long long q_stride, int window, int keep_first, float scale, float sink,
-                                  cudaStream_t stream) {
+                                  int chunk, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
+  if (chunk < 0 || (chunk > 0 && keep_first > 0)) return LLMX_REFUSED(1);
   if (H <= 0 || G <= 0 || H % G != 0 || D <= 0 || D > ATT_MAX_D || window < 0) return LLMX_REFUSED(1);
   if (Dv <= 0 || Dv > ATT_MAX_D || keep_first < 0 || q_stride < (long long)H * D) return LLMX_REFUSED(1);
   dim3 grid(n_tokens, (H + ATT_WARPS - 1) / ATT_WARPS);
@@ -111,7 +115,7 @@ LLMX_API int llmx_attention_paged(const void* q, void* out, int act_dtype, const
 #define CASE(TA, TC)                                                                                      \
   launch_pdl(attention_paged_kernel<TA, TC>, grid, dim3(ATT_WARPS * 32), smem, stream,                    \
       (const TA*)q, (TA*)out, (const TC*)k_cache, (const TC*)v_cache, block_table, table_width, token_seq, \
-      token_pos, H, G, D, Dv, (size_t)q_stride, window, keep_first, scale, sink)
+      token_pos, H, G, D, Dv, (size_t)q_stride, window, keep_first, scale, sink, chunk)
   if (act_dtype == LLMX_F32 && cache_dtype == LLMX_F32) CASE(float, float);
   else if (act_dtype == LLMX_BF16 && cache_dtype == LLMX_BF16) CASE(bf16, bf16);
   else if (act_dtype == LLMX_F32 && cache_dtype == LLMX_BF16) CASE(float, bf16);
@@ -119,4 +123,14 @@ LLMX_API int llmx_attention_paged(const void* q, void* out, int act_dtype, const
   else return LLMX_REFUSED(2);
 #undef CASE
   return LLMX_LAUNCH_STATUS();
+}
+
+LLMX_API int llmx_attention_paged(const void* q, void* out, int act_dtype, const void* k_cache,
+                                  const void* v_cache, int cache_dtype, const int* block_table, int table_width,
+                                  const int* token_seq, const int* token_pos, int n_tokens, int H, int G, int D,
+                                  int Dv, long long q_stride, int window, int keep_first, float scale, float sink,
+                                  cudaStream_t stream) {
+  return llmx_attention_paged_chunked(q, out, act_dtype, k_cache, v_cache, cache_dtype, block_table, table_width,
+                                      token_seq, token_pos, n_tokens, H, G, D, Dv, q_stride, window, keep_first, scale,
+                                      sink, 0, stream);
 }

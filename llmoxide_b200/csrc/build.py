@@ -43,6 +43,7 @@ LIBRARIES = {
     "gemm_tc": (["gemm_tc.cu"], []),
     "linear_attention": (["linear_attention.cu"], []),
     "moe": (["moe.cu"], []),
+    "post_norm": (["post_norm.cu"], []),
     "moe_tc": (["moe_tc.cu"], []),
     "short_conv": (["short_conv.cu"], []),
     "stream_mix": (["stream_mix.cu"], []),

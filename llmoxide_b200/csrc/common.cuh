@@ -199,7 +199,9 @@ template <> __device__ __forceinline__ bf16 from_f32<bf16>(float x) { return __f
 //   SILU            g sigmoid(g) * u
 //   RELU            max(g, 0) * u
 //   CLAMPED_SWISH   g' sigmoid(slope g') * (u' + shift),  g' = min(g, limit),  u' = clamp(u, -limit, limit)
-enum { LLMX_ACT_SILU = 0, LLMX_ACT_RELU = 1, LLMX_ACT_CLAMPED_SWISH = 2 };
+//   GELU_TANH       0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) * u
+enum { LLMX_ACT_SILU = 0, LLMX_ACT_RELU = 1, LLMX_ACT_CLAMPED_SWISH = 2, LLMX_ACT_GELU_TANH = 3 };
+#define LLMX_ACT_LAST LLMX_ACT_GELU_TANH
 struct GateAct {
   int kind;
   float slope, limit, shift;
@@ -207,6 +209,7 @@ struct GateAct {
 __device__ __forceinline__ float gated_act(const GateAct a, float g, float u) {
   if (a.kind == LLMX_ACT_SILU) return (g / (1.0f + expf(-g))) * u;
   if (a.kind == LLMX_ACT_RELU) return fmaxf(g, 0.f) * u;
+  if (a.kind == LLMX_ACT_GELU_TANH) return (0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)))) * u;
   g = fminf(g, a.limit);
   u = fminf(fmaxf(u, -a.limit), a.limit);
   return (g / (1.0f + expf(-a.slope * g))) * (u + a.shift);
@@ -215,6 +218,10 @@ __device__ __forceinline__ float gated_act(const GateAct a, float g, float u) {
 __device__ __forceinline__ float gated_act_fast(const GateAct a, float g, float u) {
   if (a.kind == LLMX_ACT_SILU) return __fdividef(g, 1.0f + __expf(-g)) * u;
   if (a.kind == LLMX_ACT_RELU) return fmaxf(g, 0.f) * u;
+  if (a.kind == LLMX_ACT_GELU_TANH) {       // 0.5 (1 + tanh z) = 1 / (1 + exp(-2z))
+    const float z = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return __fdividef(g, 1.0f + __expf(-2.0f * z)) * u;
+  }
   g = fminf(g, a.limit);
   u = fminf(fmaxf(u, -a.limit), a.limit);
   return __fdividef(g, 1.0f + __expf(-a.slope * g)) * (u + a.shift);

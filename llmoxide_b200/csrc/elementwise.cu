@@ -401,7 +401,7 @@ __global__ void qk_norm_rope_cache_kernel(const TIN* __restrict__ qkv, int n_spl
                                           const float* __restrict__ q_gain, const float* __restrict__ k_gain,
                                           float eps, const float* __restrict__ cos_t,
                                           const float* __restrict__ sin_t, int n_rot, int H, int G, int D,
-                                          int Dv, int write_cache) {
+                                          int Dv, int write_cache, const float* __restrict__ bias) {
   constexpr int SPW = DEEP ? 1 : QKV_SPW;
   extern __shared__ float head_buf[];
   pdl_launch_dependents();
@@ -438,6 +438,10 @@ __global__ void qk_norm_rope_cache_kernel(const TIN* __restrict__ qkv, int n_spl
         const TIN* src = tok + (size_t)(slot0 + j) * D;
         xs[j] = load4(src + d0);
         add_partials4<DEEP ? 8 : 1>(xs[j], src + split_stride + d0, n_split - 1, split_stride);
+        if (bias) {
+          const float4 bv = load4(bias + (size_t)(slot0 + j) * D + d0);
+          xs[j].x += bv.x, xs[j].y += bv.y, xs[j].z += bv.z, xs[j].w += bv.w;
+        }
       }
     }
 #pragma unroll
@@ -479,10 +483,11 @@ __global__ void qk_norm_rope_cache_kernel(const TIN* __restrict__ qkv, int n_spl
     if (slot >= n_slots) break;
     const TIN* src = slot < H + G ? tok + (size_t)slot * D : tok + (size_t)(H + G) * D + (size_t)(slot - H - G) * Dv;
     // the head's values: one tensor, or split partials added in order
+    const float* brow = bias ? bias + (src - tok) : nullptr;      // the projection's bias, a row like qkv's
     auto value = [&](int i) {
       float v = to_f32(src[i]);
       for (int s = 1; s < n_split; ++s) v += to_f32(src[s * split_stride + i]);
-      return v;
+      return brow ? v + brow[i] : v;
     };
     const bool is_q = slot < H, is_k = !is_q && slot < H + G;
     TC* cache_row = is_q ? nullptr : cache_row_of(slot);
@@ -623,17 +628,18 @@ __global__ void qk_norm_rope_cache_bf16_d128_kernel(const bf16* __restrict__ qkv
   }
 }
 
-LLMX_API int llmx_qk_norm_rope_cache(const void* qkv, int in_dtype, int n_split, long long split_stride, void* q_out,
+// bias: null, or float32 [(H+G)*D + G*Dv], added to the projected row (after its partials) before anything else.
+LLMX_API int llmx_qk_norm_rope_cache_biased(const void* qkv, int in_dtype, int n_split, long long split_stride, void* q_out,
                                      int act_dtype, void* k_cache, void* v_cache, int cache_dtype,
                                      const int* block_table, int table_width, const int* token_seq,
                                      const int* token_pos, const float* q_gain, const float* k_gain, float eps,
                                      const float* cos_t, const float* sin_t, int n_rot, int n_tokens, int H, int G,
-                                     int D, int Dv, int write_cache, cudaStream_t stream) {
+                                     int D, int Dv, int write_cache, const float* bias, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (H <= 0 || G <= 0 || D <= 0 || Dv <= 0 || n_rot < 0 || n_rot > D || (n_rot & 1) || n_split < 1) return LLMX_REFUSED(1);
   if (n_rot > 0 && (!cos_t || !sin_t)) return LLMX_REFUSED(4);
   const int n_slots = write_cache ? H + 2 * G : H;
-  if (n_split == 1 && in_dtype == LLMX_BF16 && act_dtype == LLMX_BF16 && cache_dtype == LLMX_BF16 && D == 128 &&
+  if (!bias && n_split == 1 && in_dtype == LLMX_BF16 && act_dtype == LLMX_BF16 && cache_dtype == LLMX_BF16 && D == 128 &&
       Dv == 128 && n_rot == 128 && n_tokens > 64 && !(((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15)) {
     const int per_cta = QKV_WARPS * QKV8_PER_WARP;
     launch_pdl(qk_norm_rope_cache_bf16_d128_kernel, dim3(n_tokens, (n_slots + per_cta - 1) / per_cta),
@@ -652,11 +658,11 @@ LLMX_API int llmx_qk_norm_rope_cache(const void* qkv, int in_dtype, int n_split,
     if (deep)                                                                                                      \
       launch_pdl(qk_norm_rope_cache_kernel<TIN, TA, TC, true>, grid, dim3(QKV_WARPS * 32), smem, stream,           \
         (const TIN*)qkv, n_split, (size_t)split_stride, (TA*)q_out, (TC*)k_cache, (TC*)v_cache, block_table,        \
-        table_width, token_seq, token_pos, q_gain, k_gain, eps, cos_t, sin_t, n_rot, H, G, D, Dv, write_cache);     \
+        table_width, token_seq, token_pos, q_gain, k_gain, eps, cos_t, sin_t, n_rot, H, G, D, Dv, write_cache, bias); \
     else                                                                                                           \
       launch_pdl(qk_norm_rope_cache_kernel<TIN, TA, TC, false>, grid, dim3(QKV_WARPS * 32), smem, stream,          \
         (const TIN*)qkv, n_split, (size_t)split_stride, (TA*)q_out, (TC*)k_cache, (TC*)v_cache, block_table,        \
-        table_width, token_seq, token_pos, q_gain, k_gain, eps, cos_t, sin_t, n_rot, H, G, D, Dv, write_cache);     \
+        table_width, token_seq, token_pos, q_gain, k_gain, eps, cos_t, sin_t, n_rot, H, G, D, Dv, write_cache, bias); \
   } while (0)
   const int key = in_dtype * 4 + act_dtype * 2 + cache_dtype;
   switch (key) {
@@ -672,13 +678,25 @@ LLMX_API int llmx_qk_norm_rope_cache(const void* qkv, int in_dtype, int n_split,
   return LLMX_LAUNCH_STATUS();
 }
 
+LLMX_API int llmx_qk_norm_rope_cache(const void* qkv, int in_dtype, int n_split, long long split_stride, void* q_out,
+                                     int act_dtype, void* k_cache, void* v_cache, int cache_dtype,
+                                     const int* block_table, int table_width, const int* token_seq,
+                                     const int* token_pos, const float* q_gain, const float* k_gain, float eps,
+                                     const float* cos_t, const float* sin_t, int n_rot, int n_tokens, int H, int G,
+                                     int D, int Dv, int write_cache, cudaStream_t stream) {
+  return llmx_qk_norm_rope_cache_biased(qkv, in_dtype, n_split, split_stride, q_out, act_dtype, k_cache, v_cache,
+                                        cache_dtype, block_table, table_width, token_seq, token_pos, q_gain, k_gain, eps,
+                                        cos_t, sin_t, n_rot, n_tokens, H, G, D, Dv, write_cache, nullptr, stream);
+}
+
 // ---------------------------------------------------------------------------
 // Gated activation: act[t,f] = gated_act(g, u) with g = sum_s gu[s][t,f] and
 // u = sum_s gu[s][t,F+f], in float32 (the kinds are listed in common.cuh; SiLU is x / (1 + exp(-x))).
 // ---------------------------------------------------------------------------
 template <typename TI, typename TO>
 __global__ void silu_gate_kernel(const TI* __restrict__ gu, int n_split, size_t split_stride,
-                                 TO* __restrict__ act, int n_tokens, int F, int block, const GateAct kind) {
+                                 TO* __restrict__ act, int n_tokens, int F, int block, const GateAct kind,
+                                 const float* __restrict__ bias) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t n = (size_t)n_tokens * F;
@@ -694,23 +712,25 @@ __global__ void silu_gate_kernel(const TI* __restrict__ gu, int n_split, size_t 
       g += to_f32(p[s * split_stride + gcol]);
       u += to_f32(p[s * split_stride + ucol]);
     }
+    if (bias) g += bias[gcol], u += bias[ucol];        // the projection's bias, laid out like its columns
     act[idx] = from_f32<TO>(gated_act(kind, g, u));
   }
 }
 
-LLMX_API int llmx_gate_act(const void* gu, int in_dtype, int n_split, long long split_stride, void* act,
+// bias: null, or float32 [2F] in the order of gu's columns.
+LLMX_API int llmx_gate_act_biased(const void* gu, int in_dtype, int n_split, long long split_stride, void* act,
                            int out_dtype, int n_tokens, int F, int block, int act_kind, float slope, float limit,
-                           float shift, cudaStream_t stream) {
+                           float shift, const float* bias, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (F <= 0 || n_split < 1 || block < 0 || (block > 0 && F % block)) return LLMX_REFUSED(1);
-  if (act_kind < LLMX_ACT_SILU || act_kind > LLMX_ACT_CLAMPED_SWISH) return LLMX_REFUSED(1);
+  if (act_kind < LLMX_ACT_SILU || act_kind > LLMX_ACT_LAST) return LLMX_REFUSED(1);
   const GateAct kind = {act_kind, slope, limit, shift};
   const size_t n = (size_t)n_tokens * F;
   const int threads = 256;
   const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
 #define CASE(TI, TO)                                                                                        \
   launch_pdl(silu_gate_kernel<TI, TO>, dim3(blocks), dim3(threads), 0, stream, (const TI*)gu, n_split,      \
-             (size_t)split_stride, (TO*)act, n_tokens, F, block, kind)
+             (size_t)split_stride, (TO*)act, n_tokens, F, block, kind, bias)
   if (in_dtype == LLMX_F32 && out_dtype == LLMX_F32) CASE(float, float);
   else if (in_dtype == LLMX_F32 && out_dtype == LLMX_BF16) CASE(float, bf16);
   else if (in_dtype == LLMX_BF16 && out_dtype == LLMX_BF16) CASE(bf16, bf16);
@@ -718,6 +738,13 @@ LLMX_API int llmx_gate_act(const void* gu, int in_dtype, int n_split, long long 
   else return LLMX_REFUSED(2);
 #undef CASE
   return LLMX_LAUNCH_STATUS();
+}
+
+LLMX_API int llmx_gate_act(const void* gu, int in_dtype, int n_split, long long split_stride, void* act,
+                           int out_dtype, int n_tokens, int F, int block, int act_kind, float slope, float limit,
+                           float shift, cudaStream_t stream) {
+  return llmx_gate_act_biased(gu, in_dtype, n_split, split_stride, act, out_dtype, n_tokens, F, block, act_kind, slope,
+                              limit, shift, nullptr, stream);
 }
 
 LLMX_API int llmx_silu_gate(const void* gu, int in_dtype, int n_split, long long split_stride, void* act,
@@ -776,5 +803,19 @@ LLMX_API int llmx_softcap(float* x, long long n, float cap, cudaStream_t stream)
   const long long want = (n + threads - 1) / threads;
   const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
   launch_pdl(softcap_kernel, dim3(blocks), dim3(threads), 0, stream, x, (size_t)n, cap);
+  return LLMX_LAUNCH_STATUS();
+}
+
+// x *= scale in place (a head whose logits carry a constant factor).
+__global__ void scale_kernel(float* __restrict__ x, size_t n, float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) x[i] *= scale;
+}
+
+LLMX_API int llmx_scale(float* x, long long n, float scale, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+  launch_pdl(scale_kernel, dim3(blocks), dim3(256), 0, stream, x, (size_t)n, scale);
   return LLMX_LAUNCH_STATUS();
 }

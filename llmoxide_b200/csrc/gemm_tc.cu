@@ -686,7 +686,7 @@ static int sm_count() {
 // set otherwise; kinds in common.cuh.
 static thread_local GateAct t_gate_act = {LLMX_ACT_SILU, 1.f, 0.f, 0.f};
 LLMX_API int llmx_gemm_tc_gate_act(int kind, float slope, float limit, float shift) {
-  if (kind < LLMX_ACT_SILU || kind > LLMX_ACT_CLAMPED_SWISH) return LLMX_REFUSED(1);
+  if (kind < LLMX_ACT_SILU || kind > LLMX_ACT_LAST) return LLMX_REFUSED(1);
   t_gate_act = GateAct{kind, slope, limit, shift};
   return 0;
 }

@@ -16,7 +16,8 @@
 #define MOE_MAX_TOP 16
 #define MOE_MAX_EXPERTS 1024
 
-enum { MOE_SCORE_SIGMOID = 0, MOE_SCORE_SOFTMAX = 1 };
+// SOFTMAX_TOP: the choice goes by the logits themselves, and the weights are the softmax over the chosen logits only.
+enum { MOE_SCORE_SIGMOID = 0, MOE_SCORE_SOFTMAX = 1, MOE_SCORE_SOFTMAX_TOP = 2 };
 
 // ---------------------------------------------------------------------------
 // Routing.  One warp per token.  s = sigmoid(z) (or softmax(z)).  The expert indices are cut into n_groups
@@ -49,6 +50,8 @@ __device__ __forceinline__ void moe_route_token(const float* z, float* s, float*
     for (int e = lane; e < E; e += 32) sum += expf(z[e] - m);
     sum = warp_sum(sum);
     for (int e = lane; e < E; e += 32) s[e] = expf(z[e] - m) / sum;
+  } else if (score_kind == MOE_SCORE_SOFTMAX_TOP) {
+    for (int e = lane; e < E; e += 32) s[e] = z[e];
   } else {
     for (int e = lane; e < E; e += 32) s[e] = 1.0f / (1.0f + expf(-z[e]));
   }
@@ -115,6 +118,18 @@ __device__ __forceinline__ void moe_route_token(const float* z, float* s, float*
     if (lane == k) mine = sb, my_id = bi;
     sum += sb;
   }
+  if (score_kind == MOE_SCORE_SOFTMAX_TOP) {
+    // lane k holds the k-th chosen logit: softmax over those (all lanes take part in the butterflies)
+    const float zk = lane < top ? mine : -INFINITY;
+    const float z_max = warp_max(zk);
+    const float ek = lane < top ? expf(zk - z_max) : 0.f;
+    const float total = warp_sum(ek);
+    if (lane < top) {
+      ids[lane] = my_id;
+      wts[lane] = (ek / total) * scale;
+    }
+    return;
+  }
   if (lane < top) {
     const float w = normalize ? mine / (sum + norm_eps) : mine;
     ids[lane] = my_id;
@@ -162,7 +177,8 @@ __global__ void __launch_bounds__(256)
 moe_router_kernel(const TX* __restrict__ x, long long ldx, const float* __restrict__ w, int* __restrict__ ids,
                   float* __restrict__ wts, int n_tokens, int K, int E, int top, int n_groups, int keep_groups,
                   int group_top, int score_kind, int normalize, float norm_eps, float scale, int vec,
-                  const float* __restrict__ bias, int n_extra, float* __restrict__ extra_out) {
+                  const float* __restrict__ bias, int n_extra, float* __restrict__ extra_out,
+                  const float* __restrict__ logit_bias) {
   extern __shared__ float route_smem[];            // per token: E + n_extra logits, E scores, n_groups group scores
   pdl_launch_dependents();
   pdl_wait();
@@ -201,7 +217,7 @@ moe_router_kernel(const TX* __restrict__ x, long long ldx, const float* __restri
 #pragma unroll
     for (int j = 0; j < TOK; ++j) {
       const float v = warp_sum(acc[j]);
-      if (lane == 0) route_smem[j * per_tok + e] = v;
+      if (lane == 0) route_smem[j * per_tok + e] = (logit_bias && e < E) ? v + logit_bias[e] : v;
     }
   }
   __syncthreads();
@@ -215,11 +231,13 @@ moe_router_kernel(const TX* __restrict__ x, long long ldx, const float* __restri
 }
 
 // x [T, K] (float32 or bfloat16, row stride ldx), w float32 [E, K] -> ids int32 [T, top], wts float32 [T, top].
-LLMX_API int llmx_moe_router(const void* x, int x_dtype, long long ldx, const float* w, int* ids, float* wts,
+// logit_bias: null, or float32 [E] added to the experts' logits before anything is made of them.
+LLMX_API int llmx_moe_router_biased(const void* x, int x_dtype, long long ldx, const float* w, int* ids, float* wts,
                              int n_tokens, int K, int E, int top, int n_groups, int keep_groups, int group_top,
                              int score_kind, int normalize, float norm_eps, float scale, const float* bias,
-                             int n_extra, float* extra_out, cudaStream_t stream) {
+                             int n_extra, float* extra_out, const float* logit_bias, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
+  if (score_kind < MOE_SCORE_SIGMOID || score_kind > MOE_SCORE_SOFTMAX_TOP || top > 32) return LLMX_REFUSED(1);
   if (n_extra < 0 || n_extra > 32 || (n_extra > 0 && !extra_out)) return LLMX_REFUSED(1);
   if (K <= 0 || ldx < K || E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > MOE_MAX_TOP || n_groups <= 0 || E % n_groups ||
       keep_groups <= 0 || keep_groups > n_groups || group_top <= 0 || group_top > 8 ||
@@ -232,7 +250,8 @@ LLMX_API int llmx_moe_router(const void* x, int x_dtype, long long ldx, const fl
   const int vec = (K % 8 == 0) && ((ldx * esz) % 16 == 0) && !((uintptr_t)x & 15) && !((uintptr_t)w & 15);
 #define GO(TX, TOK)                                                                                                    \
   launch_pdl(moe_router_kernel<TX, TOK>, grid, dim3(256), smem, stream, (const TX*)x, ldx, w, ids, wts, n_tokens, K, E, \
-             top, n_groups, keep_groups, group_top, score_kind, normalize, norm_eps, scale, vec, bias, n_extra, extra_out)
+             top, n_groups, keep_groups, group_top, score_kind, normalize, norm_eps, scale, vec, bias, n_extra, extra_out, \
+             logit_bias)
   if (x_dtype == LLMX_F32) {
     if (tok == 1) GO(float, 1); else GO(float, 4);
   } else if (x_dtype == LLMX_BF16) {
@@ -242,6 +261,14 @@ LLMX_API int llmx_moe_router(const void* x, int x_dtype, long long ldx, const fl
   }
 #undef GO
   return LLMX_LAUNCH_STATUS();
+}
+
+LLMX_API int llmx_moe_router(const void* x, int x_dtype, long long ldx, const float* w, int* ids, float* wts,
+                             int n_tokens, int K, int E, int top, int n_groups, int keep_groups, int group_top,
+                             int score_kind, int normalize, float norm_eps, float scale, const float* bias,
+                             int n_extra, float* extra_out, cudaStream_t stream) {
+  return llmx_moe_router_biased(x, x_dtype, ldx, w, ids, wts, n_tokens, K, E, top, n_groups, keep_groups, group_top,
+                                score_kind, normalize, norm_eps, scale, bias, n_extra, extra_out, nullptr, stream);
 }
 
 LLMX_API int llmx_moe_route(const float* logits, int* ids, float* wts, int n_tokens, int E, int top, int n_groups,
@@ -439,7 +466,7 @@ LLMX_API int llmx_moe_grouped_fma(const void* X, int x_dtype, long long ldx, con
                                   const float* pair_weight, int top, int n_tokens, int N, int K, int gated,
                                   int act_kind, float slope, float limit, float shift, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (act_kind < LLMX_ACT_SILU || act_kind > LLMX_ACT_CLAMPED_SWISH) return LLMX_REFUSED(1);
+  if (act_kind < LLMX_ACT_SILU || act_kind > LLMX_ACT_LAST) return LLMX_REFUSED(1);
   const GateAct act = {act_kind, slope, limit, shift};
   if (N <= 0 || K <= 0 || top <= 0 || max_tiles <= 0 || max_tiles > 65535 || ldx < K) return LLMX_REFUSED(1);
   if (x_dtype != w_dtype) return LLMX_REFUSED(2);
@@ -498,7 +525,7 @@ moe_extras_kernel(const TX* __restrict__ x, long long ldx, const int* __restrict
     return;
   }
   const int t = blockIdx.x - n_pairs;
-  const float gate = 1.0f / (1.0f + expf(-z[(size_t)t * ldz]));
+  const float gate = z ? 1.0f / (1.0f + expf(-z[(size_t)t * ldz])) : 1.0f;      // no logit: the result joins as it is
   float* yr = y + ((size_t)top * n_tokens + t) * d;
   for (int i = threadIdx.x * VEC; i < d; i += blockDim.x * VEC) {
     if (VEC == 8) {
@@ -521,12 +548,12 @@ moe_extras_kernel(const TX* __restrict__ x, long long ldx, const int* __restrict
 
 // x [T, d] (row stride ldx); ids, wts [T, top]; y float32 [top (+1), T, d]; identity experts are ids >= n_real
 // (n_real >= all ids: none).  shared: null, or the shared expert's result [T, d] as n_split partials, with z (one
-// float per token, ldz apart) the logit of its gate.
+// float per token, ldz apart) the logit of its gate, or null for no gate.
 LLMX_API int llmx_moe_extras(const void* x, int x_dtype, long long ldx, const int* ids, const float* wts, float* y,
                              int n_tokens, int top, int d, int n_real, const void* shared, int shared_dtype, int n_split,
                              long long split_stride, const float* z, int ldz, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (top <= 0 || d <= 0 || ldx < d || (shared && (!z || ldz < 1 || n_split < 1))) return LLMX_REFUSED(1);
+  if (top <= 0 || d <= 0 || ldx < d || (shared && ((z && ldz < 1) || n_split < 1))) return LLMX_REFUSED(1);
   const dim3 grid((unsigned)n_tokens * top + (shared ? (unsigned)n_tokens : 0u));
   // eight columns per thread and load where every row starts on a 32-byte boundary
   const bool vec = d % 8 == 0 && ldx % 8 == 0 && split_stride % 8 == 0 &&

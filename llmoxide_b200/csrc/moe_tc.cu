@@ -263,7 +263,7 @@ LLMX_API int llmx_moe_grouped_tc(const void* X, long long ldx, long long P, cons
                                  const float* sorted_weight, int N, int K, int gated, int act_kind, float slope, float limit,
                                  float shift, cudaStream_t stream) {
   if (P <= 0) return 0;
-  if (act_kind < LLMX_ACT_SILU || act_kind > LLMX_ACT_CLAMPED_SWISH) return LLMX_REFUSED(1);
+  if (act_kind < LLMX_ACT_SILU || act_kind > LLMX_ACT_LAST) return LLMX_REFUSED(1);
   const GateAct act = {act_kind, slope, limit, shift};
   if (N <= 0 || K <= 0 || (K % 8) || (ldx % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) || max_tiles <= 0 ||
       n_experts <= 0 || (!gated && (!dest || !sorted_weight)))

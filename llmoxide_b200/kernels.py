@@ -335,6 +335,24 @@ def softcap(x: torch.Tensor, cap: float) -> None:
     _check(f(_ptr(x), x.numel(), cap, _stream()), "softcap")
 
 
+def scale_(x: torch.Tensor, factor: float) -> None:
+    """x *= factor in place; x float32, contiguous."""
+    _dev(x)
+    _contig("x", x)
+    assert x.dtype == torch.float32
+    f = _fn("elementwise", "llmx_scale", [c_void_p, c_longlong, c_float, c_void_p])
+    _check(f(_ptr(x), x.numel(), factor, _stream()), "scale")
+
+
+def add_bias(y: torch.Tensor, bias: torch.Tensor) -> None:
+    """y[t, :] += bias in place (float32 sum); y [T, d] float32 or bfloat16, bias float32 [d]."""
+    _dev(y, bias)
+    _contig("y", y)
+    assert y.dim() == 2 and bias.dtype == torch.float32 and bias.numel() == y.shape[1] and bias.is_contiguous()
+    f = _fn("post_norm", "llmx_add_bias", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(y), _tag(y), y.shape[0], y.shape[1], _ptr(bias), _stream()), "add_bias")
+
+
 def add_rms_norm(h: torch.Tensor, delta, gain: torch.Tensor, eps: float, out, rows=None,
                  write_h: bool = True) -> None:
     """h float32 [T,d] is the residual stream.  ``delta`` is None or [S,T,d]
@@ -361,6 +379,40 @@ def add_rms_norm(h: torch.Tensor, delta, gain: torch.Tensor, eps: float, out, ro
              c_int, c_int, c_int, c_void_p])
     _check(f(_ptr(h), _ptr(delta), dtag, n_split, stride, _ptr(rows), n_rows, _ptr(gain), eps, _ptr(out),
              _tag(out) if out is not None else F32, d, int(write_h), _stream()), "add_rms_norm")
+
+
+def post_norm_add_norm(h, groups, bias, post_gain, post_center: bool, post_eps: float, gain, center: bool, eps: float,
+                       out, rows=None, write_h: bool = True) -> None:
+    """A sublayer's result normed before it joins the residual stream ``h`` (float32 [T, d], in place), and the norm
+    the next sublayer reads.  ``groups``: up to two (delta, weight), delta [T, d] or split partials [S, T, d] summed
+    in order; y = sum_g weight_g * delta_g + ``bias``; with ``post_gain`` y = norm(y) * post_gain; v = h + y (stored
+    when ``write_h``); with ``out`` out[r] = norm(v[rows[r]]) * gain (every row without ``rows``).  A norm with
+    ``center`` subtracts the mean (layer norm without bias), without it is an RMS norm; both are float32."""
+    deltas = [g[0] for g in groups]
+    _dev(h, bias, post_gain, gain, out, rows, *deltas)
+    assert h.dtype == torch.float32 and h.dim() == 2 and len(groups) <= 2
+    _contig("h", h)
+    d = h.shape[1]
+    args = []
+    for delta, weight in groups:
+        _contig("delta", delta)
+        if delta.dim() == 2:
+            delta = delta.unsqueeze(0)
+        assert delta.shape[1:] == h.shape, (delta.shape, h.shape)
+        args += [_ptr(delta), _tag(delta), delta.shape[0], delta.stride(0), float(weight)]
+    args += [None, F32, 1, 0, 1.0] * (2 - len(groups))
+    for v in (bias, post_gain, gain):
+        assert v is None or (v.dtype == torch.float32 and v.numel() == d and v.is_contiguous())
+    n_rows = h.shape[0] if rows is None else rows.numel()
+    if out is not None:
+        _contig("out", out)
+        assert out.shape[0] >= n_rows and out.shape[-1] == d
+    f = _fn("post_norm", "llmx_post_norm_add_norm",
+            [c_void_p, c_void_p, c_int, c_int, c_longlong, c_float, c_void_p, c_int, c_int, c_longlong, c_float, c_void_p,
+             c_void_p, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(h), *args, _ptr(bias), _ptr(post_gain), int(post_center), post_eps, _ptr(rows), n_rows, _ptr(gain),
+             int(center), eps, _ptr(out), _tag(out) if out is not None else F32, d, int(write_h), _stream()),
+           "post_norm_add_norm")
 
 
 ADD_SLICE = 512  # columns per CTA of add_gain_sumsq; the same constant as in elementwise.cu
@@ -393,8 +445,9 @@ def add_gain_sumsq(h: torch.Tensor, delta, gain: torch.Tensor, x_out: torch.Tens
 
 def qk_norm_rope_cache(qkv, q_out, k_cache, v_cache, block_table, token_seq, token_pos, q_gain, k_gain,
                        eps: float, cos, sin, n_rot: int, n_heads: int, n_kv_heads: int, head_dim: int,
-                       write_cache: bool = True, v_head_dim=None) -> None:
-    """qkv [T,(H+2G)*D], or float32 split partials [S,T,(H+2G)*D] summed in
+                       write_cache: bool = True, v_head_dim=None, bias=None) -> None:
+    """``bias`` float32, as long as a row of qkv: the projection's bias, added first.
+    qkv [T,(H+2G)*D], or float32 split partials [S,T,(H+2G)*D] summed in
     order -> q_out [T,H*D] (normed, rotated) and, when ``write_cache``, k
     (normed, rotated) and v into the paged cache entry ``k_cache``/``v_cache``
     [n_pages,G,PAGE,D] at each token's position."""
@@ -410,17 +463,19 @@ def qk_norm_rope_cache(qkv, q_out, k_cache, v_cache, block_table, token_seq, tok
     assert k_cache.dtype == v_cache.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
     if head_dim > 256 or head_dim % 2:
         raise Unsupported(f"head_dim {head_dim}: the q/k norm and rotation kernel takes even sizes up to 256")
-    f = _fn("elementwise", "llmx_qk_norm_rope_cache",
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == qkv.shape[-1] and bias.is_contiguous()
+                            and bias.is_cuda)
+    f = _fn("elementwise", "llmx_qk_norm_rope_cache_biased",
             [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
              c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-             c_int, c_int, c_int, c_void_p])
+             c_int, c_int, c_int, c_void_p, c_void_p])
     _check(f(_ptr(qkv), _tag(qkv), n_split, stride, _ptr(q_out), _tag(q_out), _ptr(k_cache), _ptr(v_cache),
              _tag(k_cache), _ptr(block_table), block_table.shape[1], _ptr(token_seq), _ptr(token_pos),
              _ptr(q_gain), _ptr(k_gain), eps, _ptr(cos), _ptr(sin), n_rot, T, n_heads, n_kv_heads, head_dim,
-             v_head_dim, int(write_cache), _stream()), "qk_norm_rope_cache")
+             v_head_dim, int(write_cache), _ptr(bias), _stream()), "qk_norm_rope_cache")
 
 
-GATE_ACTS = {"silu": 0, "relu": 1, "clamped_swish": 2}
+GATE_ACTS = {"silu": 0, "relu": 1, "clamped_swish": 2, "gelu_tanh": 3}
 
 
 def gate_act_args(activation="silu") -> tuple:
@@ -432,7 +487,7 @@ def gate_act_args(activation="silu") -> tuple:
     return GATE_ACTS[name], float(slope), float(limit), float(shift)
 
 
-def silu_gate(gu: torch.Tensor, out: torch.Tensor, block: int = 0, activation="silu") -> None:
+def silu_gate(gu: torch.Tensor, out: torch.Tensor, block: int = 0, activation="silu", bias=None) -> None:
     """gu [S,T,2F] or [T,2F] -> out [T,F] = act(gate) * up (SiLU unless ``activation`` says otherwise, see
     ``gate_act_args``).  ``block`` = 0: gate columns, then up columns; ``block`` > 0: blocks of that many gate
     columns each followed by the up columns of the same features."""
@@ -442,11 +497,13 @@ def silu_gate(gu: torch.Tensor, out: torch.Tensor, block: int = 0, activation="s
         gu = gu.unsqueeze(0)
     S, T, F2 = gu.shape
     assert out.shape == (T, F2 // 2)
-    f = _fn("elementwise", "llmx_gate_act",
+    # ``bias`` float32 [2F]: the projection's bias in the order of gu's columns, added before the activation
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == F2 and bias.is_contiguous() and bias.is_cuda)
+    f = _fn("elementwise", "llmx_gate_act_biased",
             [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float,
-             c_void_p])
+             c_void_p, c_void_p])
     _check(f(_ptr(gu), _tag(gu), S, gu.stride(0), _ptr(out), _tag(out), T, F2 // 2, block, *gate_act_args(activation),
-             _stream()), "gate_act")
+             _ptr(bias), _stream()), "gate_act")
 
 
 def sum_splits(parts: torch.Tensor, out: torch.Tensor) -> None:
@@ -462,10 +519,11 @@ def sum_splits(parts: torch.Tensor, out: torch.Tensor) -> None:
 
 def attention_paged(q, out, k_cache, v_cache, block_table, token_seq, token_pos, n_heads: int,
                     n_kv_heads: int, head_dim: int, window, scale: float, v_head_dim=None, keep_first: int = 0,
-                    sink: float = 0.0) -> None:
+                    sink: float = 0.0, chunk: int = 0) -> None:
     """General attention over the paged cache; q [T,H*D] (rows may be the first columns of wider rows), out
     [T,H*Dv].  Under a window the first ``keep_first`` keys of a sequence stay visible.  ``sink`` is added to the
-    softmax's denominator (as many keys of score 0 that have no value)."""
+    softmax's denominator (as many keys of score 0 that have no value).  With ``chunk`` n > 0 a query sees only the
+    keys of its own chunk of n positions, counted from the sequence's position 0."""
     _dev(q, out, k_cache, v_cache, block_table, token_seq, token_pos)
     _contig("out", out), _contig("block_table", block_table)
     v_head_dim = v_head_dim or head_dim
@@ -474,13 +532,13 @@ def attention_paged(q, out, k_cache, v_cache, block_table, token_seq, token_pos,
         raise Unsupported(f"head_dim {head_dim}/{v_head_dim}: the general attention kernel takes sizes up to 256")
     if n_heads % n_kv_heads:
         raise Unsupported(f"{n_heads} heads are not a multiple of {n_kv_heads} kv heads")
-    f = _fn("attention", "llmx_attention_paged",
+    f = _fn("attention", "llmx_attention_paged_chunked",
             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
-             c_int, c_int, c_int, c_int, c_int, c_longlong, c_int, c_int, c_float, c_float, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_longlong, c_int, c_int, c_float, c_float, c_int, c_void_p])
     _check(f(_ptr(q), _ptr(out), _tag(q), _ptr(k_cache), _ptr(v_cache), _tag(k_cache), _ptr(block_table),
              block_table.shape[1], _ptr(token_seq), _ptr(token_pos), q.shape[0], n_heads, n_kv_heads, head_dim,
-             v_head_dim, q.stride(0), int(window or 0), int(keep_first or 0), scale, float(sink or 0.0), _stream()),
-           "attention_paged")
+             v_head_dim, q.stride(0), int(window or 0), int(keep_first or 0), scale, float(sink or 0.0), int(chunk or 0),
+             _stream()), "attention_paged")
 
 
 def n_sm(device=None) -> int:
@@ -776,62 +834,99 @@ def _split_view(proj):
 
 def decay_scan(proj, out, state, seq_start, token_pos, seq_slot, decay, cos, sin, n_rot: int, activation: str,
                k_scale: float, n_heads: int, head_dim: int, v_head_dim: int, q_off: int, k_off: int, v_off: int,
-               max_new: int = 0, seg_len: int = 0) -> None:
+               max_new: int = 0, seg_len: int = 0, gates=None, q_scale: float = 1.0, ones_column: bool = False) -> None:
     """The recurrence S = decay_h S + k v^T, o = S^T q over every sequence's tokens of the step, in order.
     ``proj`` [T, N] (or split partials [S, T, N]) holds q heads at column ``q_off``, k heads at ``k_off``
     (``head_dim`` each) and v heads at ``v_off`` (``v_head_dim`` each); ``activation`` is applied to all three,
-    then q and k are rotated (first ``n_rot`` dims, float32 tables, at ``token_pos``) and k is scaled.  ``out`` float32
+    then q and k are rotated (first ``n_rot`` dims, float32 tables, at ``token_pos``) and scaled.  ``out`` float32
     [T, H*Dv]; ``state`` float32 [slots, H, D, Dv], read and written in place for the step's slots.  A sequence
     that brings more than ``seg_len`` tokens (0: 128) is walked in segments side by side; ``max_new`` is the most
-    tokens one sequence brings (0: not known, taken as all of them)."""
-    _dev(proj, out, state, seq_start, token_pos, seq_slot, decay, cos, sin)
+    tokens one sequence brings (0: not known, taken as all of them).
+
+    With ``gates`` (float32 [T, H, 4] as ``gate_scan`` leaves them, same ``seg_len``) decay and input weight come
+    per token: S_t = a_t S_(t-1) + b_t k_t v_t^T.  With ``ones_column`` the values get one more column that is 1
+    for every token (its state column is the sum of the weighted keys, its output q . that sum): ``out`` is then
+    [T, H*(Dv+1)], and ``state`` [slots, H, n] with n >= D*(Dv+1) floats a head, S first."""
+    _dev(proj, out, state, seq_start, token_pos, seq_slot, decay, cos, sin, gates)
     _contig("out", out), _contig("state", state)
-    assert out.dtype == torch.float32 and state.dtype == torch.float32 and decay.dtype == torch.float32
-    assert state.shape[1:] == (n_heads, head_dim, v_head_dim) and decay.numel() == n_heads
+    assert out.dtype == torch.float32 and state.dtype == torch.float32
+    assert decay is None or (decay.dtype == torch.float32 and decay.numel() == n_heads)
+    assert gates is not None or decay is not None
+    dva = v_head_dim + (1 if ones_column else 0)
+    assert out.shape[1] == n_heads * dva and state.shape[1] == n_heads
+    head_stride = state.stride(1)
+    assert head_stride >= head_dim * dva
     n_split, split_stride, row_stride = _split_view(proj)
     n_seqs, T = seq_slot.numel(), out.shape[0]
+    assert gates is None or (gates.dtype == torch.float32 and gates.is_contiguous() and gates.shape == (T, n_heads, 4))
     pad4 = lambda n: (n + 3) // 4 * 4
     # q, k and v of every (token, head) after activation, rotation and scale, float32, rows padded to 4 elements
-    prep = guard.scratch((T * n_heads * (2 * pad4(head_dim) + pad4(v_head_dim)),), torch.float32, out.device,
+    prep = guard.scratch((T * n_heads * (2 * pad4(head_dim) + pad4(dva)),), torch.float32, out.device,
                          "prepared q, k, v of the recurrence")
     max_new = max_new if 0 < max_new <= T else T
     seg = seg_len or 128
     n_seg = (max_new + seg - 1) // seg
     partial = None
     if n_seg > 1:
-        partial = guard.scratch((n_seqs * n_heads * n_seg * head_dim * v_head_dim,), torch.float32, out.device,
+        partial = guard.scratch((n_seqs * n_heads * n_seg * head_dim * dva,), torch.float32, out.device,
                                 "last states of a prompt's segments")
     f = _fn("linear_attention", "llmx_decay_scan",
             [c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_int, c_int,
-             c_int, c_int, c_int, c_int, c_void_p])
+             c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_float, c_int, c_void_p])
     _check(f(_ptr(proj), _tag(proj), n_split, split_stride, row_stride, q_off, k_off, v_off, _ptr(prep), _ptr(out),
              _ptr(state), _ptr(partial), _ptr(seq_start), _ptr(token_pos), _ptr(seq_slot), _ptr(decay), _ptr(cos),
              _ptr(sin), n_rot, _ACTS[activation], k_scale, T, n_seqs, max_new, seg, n_heads, head_dim, v_head_dim,
-             n_sm(out.device), _stream()), "decay_scan")
+             n_sm(out.device), _ptr(gates), head_stride, q_scale, int(ones_column), _stream()), "decay_scan")
     global launch_count
     launch_count += 2 if n_seg > 1 else 1          # beside the preparation: the recurrence, and the segments' second pass
 
 
+def gate_scan(proj, i_off: int, f_off: int, bias_i, bias_f, cap: float, gates, state, m_off: int, seq_start, seq_slot,
+              n_heads: int, seg_len: int = 0) -> None:
+    """The gates of a recurrence with a running maximum, per (sequence, head) over the step's tokens in order:
+    i = cap tanh((proj[:, i_off + h] + bias_i[h]) / cap), f = logsigmoid(cap tanh((proj[:, f_off + h] + bias_f[h]) /
+    cap)) (``cap`` <= 0: no cap), m_t = max(f_t + m_(t-1), i_t).  ``gates`` float32 [T, H, 4] receives a_t =
+    exp(f_t + m_(t-1) - m_t), b_t = exp(i_t - m_t), exp(-m_t) and the product of a over the token's segment so far
+    (segments of ``seg_len`` tokens, 0: 128, counted from the sequence's first token of the step).  m lives in
+    ``state`` [slots, H, n] at ``m_off`` floats into a head's state and is moved on in place."""
+    _dev(proj, bias_i, bias_f, gates, state, seq_start, seq_slot)
+    _contig("gates", gates), _contig("state", state)
+    assert gates.dtype == torch.float32 and state.dtype == torch.float32 and state.shape[1] == n_heads
+    assert all(b is None or (b.dtype == torch.float32 and b.numel() == n_heads and b.is_contiguous()) for b in (bias_i, bias_f))
+    n_split, split_stride, row_stride = _split_view(proj)
+    f = _fn("linear_attention", "llmx_gate_scan",
+            [c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+             c_longlong, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(proj), _tag(proj), n_split, split_stride, row_stride, i_off, f_off, _ptr(bias_i), _ptr(bias_f),
+             float(cap or 0.0), _ptr(gates), _ptr(state), state.stride(1), m_off, _ptr(seq_start), _ptr(seq_slot),
+             seq_slot.numel(), n_heads, seg_len or 128, _stream()), "gate_scan")
+
+
 def gated_norm(o, proj, g_off: int, gain, eps: float, gate: str, per_head: bool, y, n_heads: int,
-               v_head_dim: int) -> None:
+               v_head_dim: int, gates=None, den_eps: float = 0.0) -> None:
     """y = o / sqrt(mean(o^2) + eps) * gain * gate(proj[:, g_off:]) with the mean over one head's columns
-    (``per_head``) or over the whole row; o float32 [T, H*Dv]; ``gain`` float32 [H*Dv] or None."""
-    _dev(o, proj, gain, y)
+    (``per_head``) or over the whole row; o float32 [T, H*Dv]; ``gain`` float32 [H*Dv] or None.  With ``gates``
+    (``gate_scan``'s, per_head only) o is [T, H*(Dv+1)], a head's last column being n . q, and o is first divided
+    by max(|n . q|, exp(-m)) + ``den_eps``."""
+    _dev(o, proj, gain, y, gates)
     _contig("o", o), _contig("y", y)
-    assert o.dtype == torch.float32 and y.shape == o.shape and (gain is None or gain.dtype == torch.float32)
+    assert o.dtype == torch.float32 and (gain is None or gain.dtype == torch.float32)
+    assert y.shape == (o.shape[0], n_heads * v_head_dim)
+    assert o.shape[1] == n_heads * (v_head_dim + (1 if gates is not None else 0))
     n_split, split_stride, row_stride = _split_view(proj)
     f = _fn("linear_attention", "llmx_gated_norm",
             [c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p, c_float, c_int, c_int, c_void_p,
-             c_int, c_int, c_int, c_int, c_void_p])
+             c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p])
     _check(f(_ptr(o), _ptr(proj), _tag(proj), n_split, split_stride, row_stride, g_off, _ptr(gain), eps, _ACTS[gate],
-             int(per_head), _ptr(y), _tag(y), o.shape[0], n_heads, v_head_dim, _stream()), "gated_norm")
+             int(per_head), _ptr(y), _tag(y), o.shape[0], n_heads, v_head_dim, _ptr(gates), den_eps, _stream()),
+           "gated_norm")
 
 
 # ---- routed experts ------------------------------------------------------------------------------------
 
 MOE_TILE = 64          # rows per tile of the grouped products; the same constant as in moe.cu
-_SCORES = {"sigmoid": 0, "softmax": 1}
+_SCORES = {"sigmoid": 0, "softmax": 1, "softmax_top": 2}
 
 
 def moe_route(logits, ids, weights, top: int, n_groups: int, keep_groups: int, group_top: int, score: str,
@@ -871,23 +966,27 @@ def moe_sort(ids, n_experts: int, perm, tiles, tile_rows: int = MOE_TILE, pair_w
 
 
 def moe_router(x, w, ids, weights, n_groups: int, keep_groups: int, group_top: int, score: str, normalize: bool,
-               norm_eps: float, scale: float, bias=None, extra_out=None) -> None:
+               norm_eps: float, scale: float, bias=None, extra_out=None, logit_bias=None) -> None:
     """The router's product (float32 ``w`` [E, K] times the rows of ``x``, float32 sums) and the routing of
     ``moe_route`` in one kernel.  With ``extra_out`` float32 [T, n], ``w`` holds n more rows behind the experts',
-    whose products are written there as they are."""
-    _dev(x, w, ids, weights, bias, extra_out)
+    whose products are written there as they are.  ``logit_bias`` float32 [E] joins the experts' logits before the
+    scores are made.  ``score`` "softmax_top": the largest logits win, and the weights are the softmax over the
+    winners' logits only."""
+    _dev(x, w, ids, weights, bias, extra_out, logit_bias)
+    assert logit_bias is None or (logit_bias.dtype == torch.float32 and logit_bias.is_contiguous()
+                                  and logit_bias.numel() == w.shape[0] - (0 if extra_out is None else extra_out.shape[1]))
     n_extra = 0 if extra_out is None else extra_out.shape[1]
     assert extra_out is None or (extra_out.dtype == torch.float32 and extra_out.is_contiguous())
     assert bias is None or (bias.dtype == torch.float32 and bias.numel() == w.shape[0] - n_extra and bias.is_contiguous())
     _contig("w", w), _contig("ids", ids), _contig("weights", weights)
     assert w.dtype == torch.float32 and x.stride(1) == 1 and ids.dtype == torch.int32 and weights.dtype == torch.float32
     T, top = ids.shape
-    f = _fn("moe", "llmx_moe_router",
+    f = _fn("moe", "llmx_moe_router_biased",
             [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-             c_int, c_int, c_float, c_float, c_void_p, c_int, c_void_p, c_void_p])
+             c_int, c_int, c_float, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p])
     _check(f(_ptr(x), _tag(x), x.stride(0), _ptr(w), _ptr(ids), _ptr(weights), T, x.shape[1], w.shape[0] - n_extra, top,
              n_groups, keep_groups, group_top, _SCORES[score], int(normalize), norm_eps, scale, _ptr(bias), n_extra,
-             _ptr(extra_out), _stream()), "moe_router")
+             _ptr(extra_out), _ptr(logit_bias), _stream()), "moe_router")
 
 
 def moe_tc_supports(x, w) -> bool:
@@ -948,7 +1047,7 @@ def moe_grouped(x, w, y, perm, tiles, pair_weight, top: int, n_tokens: int, gate
 def moe_extras(x, ids, weights, y, n_real: int, shared=None, shared_z=None) -> None:
     """What the grouped products leave out, in one launch.  Identity experts: y[choice, t, :] = weights[t, choice] *
     x[t, :] for every pair whose expert id is ``n_real`` or more (an identity expert's output is its input); the other
-    pairs' rows are left alone.  A shared expert: y[top, t, :] = sigmoid(shared_z[t]) * shared[t, :] (``shared``
+    pairs' rows are left alone.  A shared expert: y[top, t, :] = sigmoid(shared_z[t]) * shared[t, :], or shared[t, :] itself without ``shared_z`` (``shared``
     [T, d] or partials [P, T, d]; ``shared_z`` float32, one number per token, a column of a wider row allowed).
     y float32 [top (+1), T, d]."""
     _dev(x, ids, weights, y, shared, shared_z)
@@ -962,8 +1061,10 @@ def moe_extras(x, ids, weights, y, n_real: int, shared=None, shared_z=None) -> N
         _contig("shared", shared)
         if shared.dim() == 2:
             shared = shared.unsqueeze(0)
-        assert shared.shape[1:] == (T, d) and shared_z.dtype == torch.float32 and shared_z.dim() == 1 and shared_z.numel() == T
-        n_split, stride, stag, ldz = shared.shape[0], shared.stride(0), _tag(shared), shared_z.stride(0)
+        assert shared.shape[1:] == (T, d)
+        assert shared_z is None or (shared_z.dtype == torch.float32 and shared_z.dim() == 1 and shared_z.numel() == T)
+        n_split, stride, stag = shared.shape[0], shared.stride(0), _tag(shared)
+        ldz = 1 if shared_z is None else shared_z.stride(0)
     f = _fn("moe", "llmx_moe_extras",
             [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int,
              c_longlong, c_void_p, c_int, c_void_p])

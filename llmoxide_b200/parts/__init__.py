@@ -2,8 +2,8 @@
 position encodings and their arrangement in a block.  Each takes its sizes
 and constants as parameters; none knows which model it is in."""
 
-from . import (attention, block, embedding, experts, feed_forward, head, linear_attention, norm,  # noqa: F401
-               position)  # noqa: F401  (register the built-in kinds)
+from . import (attention, block, embedding, experts, feed_forward, head, linear_attention, mlstm, norm,  # noqa: F401
+               position, side_by_side)  # noqa: F401  (register the built-in kinds)
 from .block import build_block
 from .linear import Linear
 from .registry import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS,

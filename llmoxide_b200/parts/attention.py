@@ -27,6 +27,14 @@ sink of score 0 that has no value).  ``v_mix``: "source" leaves this call's
 values (after the convolution) for later calls of the step under the name
 ``v_mix_key``; "mix" replaces its values by (1 - l) v + l v_source with the
 learned scalar l (tensor ``v_mix``) before they are cached.
+
+``chunk`` n > 0: positions are cut into chunks of n, counted from position 0 of
+the sequence, and a query sees the keys j <= p of its own chunk only
+(floor(j / n) = floor(p / n)); the cache entry keeps what a window of n would.
+Tensors ``q_bias``, ``k_bias``, ``v_bias``, ``o_bias``: biases of the four
+projections (q, k, v: added where the projected row is read, before norm and
+rotation; o: offered as ``out_bias`` to an arrangement that adds it in its
+norm kernel, else added here).
 """
 
 from __future__ import annotations
@@ -49,15 +57,20 @@ class GQAttention:
         self.Dv = spec.get("v_head_dim") or self.D
         self.window = spec.get("window")
         self.keep_first = int(spec.get("keep_first") or 0) if self.window else 0
+        self.chunk = int(spec.get("chunk") or 0)
+        if self.chunk and (self.window or not bool(spec.get("own_kv", True))):
+            raise Unsupported("a chunked mask is built for a layer with its own keys and values and no window")
         # what the cache entry holds: this layer's own mask unless the description names a wider one
         self.cache_window = spec.get("cache_window", self.window) if "cache_window" in spec.params else self.window
+        if self.chunk:
+            self.cache_window = self.chunk           # nothing before the last `chunk` positions is seen again
         self.cache_keep_first = int(spec.get("cache_keep_first", self.keep_first) or 0) if self.cache_window else 0
         self.own_kv = bool(spec.get("own_kv", True))
         self.eps = float(spec.get("qk_norm_eps") or 0.0)
         if self.H % self.G:
             raise Unsupported(f"{self.H} heads are not a multiple of {self.G} kv heads")
         # the shape the tiled kernels are written for; every other one goes to the general kernel
-        self.plain = self.Dv == self.D and self.D % 16 == 0
+        self.plain = self.Dv == self.D and self.D % 16 == 0 and not self.chunk
         if max(self.D, self.Dv) > 256:
             raise Unsupported(f"head sizes {self.D}/{self.Dv}: the attention kernels take sizes up to 256")
         t = spec.tensors
@@ -73,7 +86,14 @@ class GQAttention:
         else:
             self.qkv = None
             self.q_only = Linear(weights.pop(t["q"].name), rt)
-        self.o = Linear(weights.pop(t["o"].name), rt)
+        self.o = Linear(weights.pop(t["o"].name), rt, bias=weights.pop(t["o_bias"].name) if "o_bias" in t else None)
+        self.out_bias, self.defer_out_bias = self.o.bias, False
+        self.qkv_bias = None
+        if "q_bias" in t:
+            if not self.own_kv:
+                raise Unsupported("projection biases are built for a layer with its own keys and values")
+            self.qkv_bias = torch.cat([weights.pop(t[r].name).to(torch.float32) for r in ("q_bias", "k_bias", "v_bias")]
+                                      ).contiguous()
         self.q_gain = self.k_gain = None
         if "q_norm" in t:
             self.q_gain = weights.pop(t["q_norm"].name).to(torch.float32).contiguous()
@@ -85,6 +105,8 @@ class GQAttention:
         if self.v_mix not in (None, "source", "mix"):
             raise Unsupported(f"v_mix {self.v_mix!r}: 'source' or 'mix'")
         self.conv_w = self.v_lambda = None
+        if self.qkv_bias is not None and (self.taps or self.v_mix):
+            raise Unsupported("projection biases beside a short convolution or mixed values are not built")
         if self.taps:
             if not self.own_kv or self.q_gain is not None:
                 raise Unsupported("the short convolution is built for a layer with its own keys and values and no q/k norm")
@@ -148,12 +170,14 @@ class GQAttention:
                                     n_rot, v_first, self.v_lambda, mode, H, G, D, Dv, inline_state=inline)
             if not inline:
                 kernels.conv_state_update(qkv, view.state, self.taps, ctx)
-        elif not writes_cache and self.q_gain is None and n_rot == 0:
+        elif not writes_cache and self.q_gain is None and n_rot == 0 and self.qkv_bias is None:
             # A call that reads another call's cache entry makes only queries; nothing is done to them.
             q = self.q_only(x, out_dtype=self.rt.act_dtype)
         else:
             if writes_cache:
                 qkv = self.qkv(x, splits_ok=True)
+            elif self.qkv_bias is not None:
+                raise Unsupported("a layer with projection biases owns its cache entry")
             else:
                 q_part = self.q_only(x)
                 qkv = torch.empty((T, (H + G) * D + G * Dv), dtype=q_part.dtype, device=dev)
@@ -161,12 +185,12 @@ class GQAttention:
             q = torch.empty((T, H * D), dtype=self.rt.act_dtype, device=dev)
             kernels.qk_norm_rope_cache(qkv, q, view.k, view.v, block_table, ctx.token_seq, ctx.token_pos,
                                        self.q_gain, self.k_gain, self.eps, cos, sin, n_rot, H, G, D, writes_cache,
-                                       v_head_dim=Dv)
+                                       v_head_dim=Dv, bias=self.qkv_bias)
         out = torch.empty((T, H * Dv), dtype=self.rt.act_dtype, device=dev)
         self.attend(q, out, view, block_table, ctx)
-        if residual is not None and self.o.add_into(out, residual):
+        if self.out_bias is None and residual is not None and self.o.add_into(out, residual):
             return None
-        return self.o(out, splits_ok=True)
+        return self.o(out, splits_ok=True, add_bias=not self.defer_out_bias)
 
     def attend(self, q, out, view, block_table, ctx):
         """bfloat16: the split-key kernel when every sequence brings one token;
@@ -191,4 +215,4 @@ class GQAttention:
         else:
             kernels.attention_paged(q, out, view.k, view.v, block_table, ctx.token_seq, ctx.token_pos,
                                     H, G, D, self.window, self.scale, v_head_dim=self.Dv, keep_first=self.keep_first,
-                                    sink=self.sink)
+                                    sink=self.sink, chunk=self.chunk)

@@ -8,7 +8,11 @@ that follows it, so a block hands its last delta on as ``pending`` instead of
 adding it itself.  ``parallel`` is the block with one norm whose output both
 sublayers read: h += mixer(norm(h)) + feed_forward(norm(h)).  A mixer or feed-forward with ``adds_to_residual`` is given the
 stream (``residual=h``) and may add its result there itself, in the kernel of its
-last product; it then returns None, and the norm that follows has nothing to add."""
+last product; it then returns None, and the norm that follows has nothing to add.
+``sandwich`` norms a sublayer's result as well as its input: h += norm_b(mixer(norm_a(h))), then the same around
+the feed-forward; the norm behind a sublayer, the residual add and the norm before the next sublayer are one kernel.
+A part whose last product has a bias offers it as ``out_bias``; an arrangement that can add it in its own norm
+kernel sets the part's ``defer_out_bias``, and the part then leaves the bias to it."""
 
 from __future__ import annotations
 
@@ -67,6 +71,9 @@ class PreNormBlock:
 
 def _summed(delta):
     """A delta as one tensor: split partials [S,T,d] are added in order."""
+    from .norm import WeightedSum
+    if isinstance(delta, WeightedSum):
+        return sum(w * _summed(t).float() for t, w in delta.terms)
     if delta.dim() == 2:
         return delta
     out = torch.empty(delta.shape[1:], dtype=torch.float32, device=delta.device)
@@ -200,3 +207,58 @@ def _with_mult(norm_spec, mult: float):
     """The norm's description with the factor on its sublayer's result."""
     from ..config.spec import PartSpec
     return PartSpec(norm_spec.kind, dict(norm_spec.params, residual_mult=mult), norm_spec.tensors)
+
+
+@register_arrangement("sandwich")
+class SandwichBlock:
+    """A norm before and a norm behind each sublayer: h += post(mixer(pre(h))), then h += post(feed_forward(pre(h)))
+    (norms ``mixer``, ``mixer_post``, ``feed_forward``, ``feed_forward_post``; a layer without a feed-forward has the
+    first two).  The normed result is owed to the next norm before a sublayer, whose kernel norms it, adds it to the
+    float32 stream and norms the stream in one pass over the row; the sublayers' output biases ride along."""
+
+    def __init__(self, spec, weights: dict, rt):
+        position = None
+        if spec.position is not None:
+            position = rt_shared_position(spec.position, weights, rt)
+        self.mixer_norm = build_part(NORMS, "norm", spec.norms["mixer"], weights, rt)
+        self.mixer_post = build_part(NORMS, "norm", spec.norms["mixer_post"], weights, rt)
+        self.mixer = lookup(MIXERS, "mixer", spec.mixer.kind)(spec.mixer, position, weights, rt)
+        self.feed_forward = build_part(FEED_FORWARDS, "feed-forward", spec.feed_forward, weights, rt)
+        self.ff_norm = self.ff_post = None
+        if "feed_forward" in spec.norms:
+            self.ff_norm = build_part(NORMS, "norm", spec.norms["feed_forward"], weights, rt)
+            self.ff_post = build_part(NORMS, "norm", spec.norms["feed_forward_post"], weights, rt)
+        for part in (self.mixer, self.feed_forward):
+            if getattr(part, "out_bias", None) is not None:
+                part.defer_out_bias = True           # added by the norm kernel behind the part
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def libraries(self) -> set:
+        libs = set()
+        for part in (self.mixer_norm, self.mixer_post, self.ff_norm, self.ff_post, self.mixer, self.feed_forward):
+            if part is not None:
+                libs |= getattr(part, "libraries", set)()
+        return libs
+
+    def forward(self, h, pending, ctx, view, writes_cache=True):
+        probe = getattr(ctx, "probe", None)
+        if probe:
+            self.mixer_norm.add(h, pending)
+            pending = None
+            probe("resid_in", h)
+        x = self.mixer_norm.add_forward(h, pending)
+        a = self.mixer.forward(x, ctx, view, writes_cache)
+        if probe:
+            probe("attn_norm", x), probe("attn_output", _summed(a))
+        pending = self.mixer_post.owed(a, bias=getattr(self.mixer, "out_bias", None))
+        if self.ff_norm is None:
+            return pending
+        x = self.ff_norm.add_forward(h, pending)
+        out = self.feed_forward.forward(x, ctx)
+        if probe:
+            probe("attn_residual", h), probe("attn_post_norm", x)
+            if out is not None:
+                probe("ffn_out", _summed(out))
+        return self.ff_post.owed(out, bias=getattr(self.feed_forward, "out_bias", None))

@@ -2,8 +2,10 @@
 small gated layers, down(act(gate x) * (up x)), weighted by the router.
 
 Router logits z = W_r x are float32 (the router's matrix is kept in float32;
-x may be the compute dtype's rounding).  ``score``: s = sigmoid(z), or a
-softmax over z.  With ``n_groups`` > 1 the expert indices are cut into
+x may be the compute dtype's rounding), plus the tensor ``router_bias`` when
+there is one.  ``score``: s = sigmoid(z), or a softmax over z, or
+"softmax_top": the ``top`` largest z win and their weights are the softmax
+over those z alone.  With ``n_groups`` > 1 the expert indices are cut into
 ``n_groups`` contiguous blocks of equal length; every block is ranked by the
 sum of its ``group_score_top`` highest s, and a token's choice is restricted
 to the ``keep_groups`` top-ranked blocks.  The ``top`` highest s among the
@@ -16,7 +18,8 @@ identity experts: they have no tensors and their output is the input itself
 (``kernels.gate_act_args``; "clamped_swish" takes ``act_slope``, ``act_limit``,
 ``act_up_shift``).  A shared expert (``shared_size``; tensors ``shared_gate``,
 ``shared_up``, ``shared_down``, ``shared_sg`` [1, d]; its limit ``shared_limit``)
-runs for every token and is added times sigmoid(shared_sg . x).
+runs for every token and is added times sigmoid(shared_sg . x), or as it is
+when there is no ``shared_sg``.
 
 The step's (token, choice) pairs are ordered by expert on the device and the
 two products run grouped over that order (csrc/moe.cu), so nothing is read
@@ -76,11 +79,14 @@ class RoutedExperts:
         self.router = weights.pop(t["router"].name).to(torch.float32).contiguous()
         self.correction = (weights.pop(t["correction"].name).to(torch.float32).contiguous()
                            if "correction" in t else None)
-        self.shared = None
+        self.router_bias = (weights.pop(t["router_bias"].name).to(torch.float32).contiguous()
+                            if "router_bias" in t else None)
+        self.shared, self.shared_gated = None, "shared_sg" in t
         if spec.get("shared_size"):
-            # the shared expert's gate reads the same rows as the router: its vector is one more row of that matrix
-            self.router = torch.cat([self.router, weights.pop(t["shared_sg"].name).to(torch.float32).reshape(1, -1)],
-                                    dim=0).contiguous()
+            if self.shared_gated:
+                # the shared expert's gate reads the same rows as the router: its vector is one more row of that matrix
+                self.router = torch.cat([self.router, weights.pop(t["shared_sg"].name).to(torch.float32).reshape(1, -1)],
+                                        dim=0).contiguous()
             # the shared expert itself is a gated feed-forward of this package, with the experts' activation
             from ..config.spec import PartSpec
             from .feed_forward import GatedMLP
@@ -116,9 +122,10 @@ class RoutedExperts:
         P = T * self.top
         ids = torch.empty((T, self.top), dtype=torch.int32, device=dev)
         pair_w = torch.empty((T, self.top), dtype=torch.float32, device=dev)
-        shared_z = torch.empty((T, 1), dtype=torch.float32, device=dev) if self.shared else None
+        shared_z = torch.empty((T, 1), dtype=torch.float32, device=dev) if self.shared and self.shared_gated else None
         kernels.moe_router(x, self.router, ids, pair_w, self.n_groups, self.keep_groups, self.group_top, self.score,
-                           self.normalize, self.norm_eps, self.scale, bias=self.correction, extra_out=shared_z)
+                           self.normalize, self.norm_eps, self.scale, bias=self.correction, extra_out=shared_z,
+                           logit_bias=self.router_bias)
         perm = torch.empty((P,), dtype=torch.int32, device=dev)
         fast = self.tensor_cores and x.dtype == torch.bfloat16 and kernels.moe_tc_supports(x, self.gate_up)
         rows = self.tile_rows(P) if fast else kernels.MOE_TILE
@@ -144,5 +151,5 @@ class RoutedExperts:
             # an identity expert's output is the token's own row times the weight; the shared expert's result is
             # weighted by its gate: both join y in one launch
             shared = self.shared.forward(x, ctx) if self.shared else None
-            kernels.moe_extras(x, ids, pair_w, y, self.E, shared, shared_z[:, 0] if self.shared else None)
+            kernels.moe_extras(x, ids, pair_w, y, self.E, shared, shared_z[:, 0] if shared_z is not None else None)
         return y

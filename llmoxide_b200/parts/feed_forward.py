@@ -1,8 +1,12 @@
 """Gated feed-forward: down(act(gate x) * (up x)), act = SiLU x/(1+exp(-x))
 (crates/model/src/qwen35/cpu.rs:386-395, crates/model/src/ops.rs:176-178).
 Gate and up are one matrix product over the rows [gate; up].  ``activation``
-may also be "relu", or ("clamped_swish", slope, limit, shift):
-min(g, limit) * sigmoid(slope * min(g, limit)) * (clamp(u, -limit, limit) + shift)."""
+may also be "relu", "gelu_tanh" (0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))), or
+("clamped_swish", slope, limit, shift):
+min(g, limit) * sigmoid(slope * min(g, limit)) * (clamp(u, -limit, limit) + shift).
+Tensors ``gate_bias``, ``up_bias``, ``down_bias``: biases of the three projections (gate and up: added where the
+activation reads the product; down: offered as ``out_bias`` to an arrangement that adds it in its norm kernel,
+else added here)."""
 
 from __future__ import annotations
 
@@ -50,7 +54,15 @@ class GatedMLP:
         del wg, wu
         self.gate_up = Linear(fused, rt)
         del fused
-        self.down = Linear(weights.pop(t["down"].name), rt)
+        self.gu_bias = None
+        if "gate_bias" in t:
+            bg, bu = (weights.pop(t[r].name).to(torch.float32) for r in ("gate_bias", "up_bias"))
+            # in the order of the fused matrix's rows
+            self.gu_bias = (torch.stack([bg.view(-1, 16), bu.view(-1, 16)], dim=1).reshape(-1) if self.block
+                            else torch.cat([bg, bu])).contiguous()
+        self.down = Linear(weights.pop(t["down"].name), rt,
+                           bias=weights.pop(t["down_bias"].name) if "down_bias" in t else None)
+        self.out_bias, self.defer_out_bias = self.down.bias, False
 
     def libraries(self) -> set:
         return {"elementwise"} | self.gate_up.libraries() | self.down.libraries()
@@ -58,7 +70,8 @@ class GatedMLP:
     @property
     def takes_row_scales(self) -> bool:
         """The gate|up product can apply a norm's row scales in its epilogue, ahead of the activation."""
-        return self.gate_up._tc is not None and kernels.gemm_tc_gated_supports(self.activation)
+        return (self.gate_up._tc is not None and kernels.gemm_tc_gated_supports(self.activation)
+                and self.gu_bias is None)
 
     adds_to_residual = True      # forward() takes ``residual`` and may return None: "already added"
 
@@ -66,7 +79,7 @@ class GatedMLP:
         tc = self.gate_up._tc
         scaled = isinstance(x, RowScaled)
         n_tokens = x.shape[0]
-        if tc is not None and x.dtype == torch.bfloat16 and n_tokens > FUSE_MIN_TOKENS and (
+        if tc is not None and self.gu_bias is None and x.dtype == torch.bfloat16 and n_tokens > FUSE_MIN_TOKENS and (
                 scaled or kernels.gemm_tc_supports(x, tc.weight)) and kernels.gemm_tc_gated_supports(self.activation):
             # the activation is the epilogue of the gate/up product
             act = tc.gated(x, self.rt.act_dtype, self.block, self.activation)
@@ -74,7 +87,7 @@ class GatedMLP:
             assert not scaled
             gu = self.gate_up(x, splits_ok=True)
             act = torch.empty((n_tokens, self.F), dtype=self.rt.act_dtype, device=x.device)
-            kernels.silu_gate(gu, act, self.block, self.activation)
-        if residual is not None and self.down.add_into(act, residual):
+            kernels.silu_gate(gu, act, self.block, self.activation, bias=self.gu_bias)
+        if self.out_bias is None and residual is not None and self.down.add_into(act, residual):
             return None
-        return self.down(act, splits_ok=True)
+        return self.down(act, splits_ok=True, add_bias=not self.defer_out_bias)

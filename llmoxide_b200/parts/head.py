@@ -1,8 +1,8 @@
 """The head: logits = x W^T in float32 over the wanted rows only, W the
 head's own matrix or, tied, the embedding's table
 (crates/model/src/qwen35/cpu.rs:406-416, crates/model/src/qwen35/weights.rs:79);
-with ``softcap`` c the logits become c * tanh(logits / c) (the dense Qwen3
-description gives none)."""
+with ``scale`` s the logits are multiplied by s, and with ``softcap`` c they
+become c * tanh(logits / c) after that (the dense Qwen3 description gives neither)."""
 
 from __future__ import annotations
 
@@ -28,6 +28,8 @@ class LinearHead:
         self.linear = Linear(weight, rt)
         cap = spec.get("softcap")
         self.softcap = None if cap is None else float(cap)
+        scale = spec.get("scale")
+        self.scale = None if scale is None or float(scale) == 1.0 else float(scale)
 
     def libraries(self) -> set:
         return {"elementwise"} | self.linear.libraries()
@@ -37,6 +39,8 @@ class LinearHead:
         if logits.dim() == 3:       # split partials of the reduction
             parts, logits = logits, torch.empty(logits.shape[1:], dtype=torch.float32, device=x.device)
             kernels.sum_splits(parts, logits)
+        if self.scale is not None:
+            kernels.scale_(logits, self.scale)
         if self.softcap is not None:
             kernels.softcap(logits, self.softcap)
         return logits

@@ -14,9 +14,13 @@ from .runtime import Runtime
 
 
 class Linear:
-    def __init__(self, weight: torch.Tensor, rt: Runtime):
+    def __init__(self, weight: torch.Tensor, rt: Runtime, bias=None):
+        """``bias`` (optional, [out]): kept in float32.  Whoever can add it in a kernel that reads the product
+        anyway calls with ``add_bias=False`` and hands ``self.bias`` to that kernel; otherwise it is added here."""
         assert weight.dim() == 2 and weight.stride(1) == 1
         self.weight, self.rt = weight, rt
+        self.bias = None if bias is None else bias.to(torch.float32).contiguous()
+        assert self.bias is None or self.bias.numel() == weight.shape[0]
         self.out_features, self.in_features = weight.shape
         self._tc = None
         if rt.tensor_cores and weight.dtype == torch.bfloat16 and rt.dtype == "bfloat16":
@@ -24,9 +28,16 @@ class Linear:
             self._tc = linear_tc.plan_for(weight, rt.n_sm)
 
     def libraries(self) -> set:
-        return {"gemm_tc", "elementwise"} if self._tc is not None else {"gemm_fma"}
+        libs = {"gemm_tc", "elementwise"} if self._tc is not None else {"gemm_fma"}
+        return libs | ({"post_norm"} if self.bias is not None else set())
 
-    def __call__(self, x, out_dtype=None, splits_ok: bool = False):
+    def __call__(self, x, out_dtype=None, splits_ok: bool = False, add_bias: bool = True):
+        out = self._product(x, out_dtype, splits_ok)
+        if self.bias is not None and add_bias:
+            kernels.add_bias(out if out.dim() == 2 else out[0], self.bias)      # (partials: once, on the first)
+        return out
+
+    def _product(self, x, out_dtype=None, splits_ok: bool = False):
         """x [T, in] -> [T, out], or split partials [S, T, out] in float32 when
         ``splits_ok`` and the kernel chose to split the reduction.  ``x`` may be
         ``RowScaled`` (tensor-core path only; see ``parts.row_scaled``)."""

@@ -9,7 +9,14 @@ three weights ride with the norm (tensors ``hc_in`` [S], ``hc_out`` [S],
 ``mult``); without them the norm reads the plain sum and the result is added
 to every copy times ``mult``.  As with one stream, the update is applied by
 the next norm's kernel: ``owed(y)`` wraps a sublayer's result into the
-``StreamUpdate`` that the next ``add_forward`` (or ``add``) takes as ``delta``."""
+``StreamUpdate`` that the next ``add_forward`` (or ``add``) takes as ``delta``.
+
+``layer_norm`` is the norm with the mean taken off and no bias,
+(x - mean) / sqrt(mean((x - mean)^2) + eps) * g.  Either norm can also stand
+BEHIND a sublayer ("sandwich" blocks, h += norm_b(f(norm_a(h)))): ``owed(y)``
+then wraps the sublayer's result into a ``PostNormed``, and the next norm's
+kernel norms it, adds it to the stream and norms the stream in one pass.  Two
+mixers side by side hand over a ``WeightedSum`` of their results."""
 
 from __future__ import annotations
 
@@ -29,6 +36,75 @@ class StreamUpdate:
         self.delta, self.mix, self.write = delta, mix, write
 
 
+class WeightedSum:
+    """Several results that join the stream as sum_g weight_g * delta_g (each delta [T,d] or partials [S,T,d])."""
+
+    __slots__ = ("terms",)
+
+    def __init__(self, terms):
+        self.terms = list(terms)          # [(delta, weight)], at most two
+
+
+class PostNormed:
+    """What a sublayer owes the residual stream when its result is normed first:
+    h += norm(sum_g weight_g * delta_g + bias) * gain."""
+
+    __slots__ = ("terms", "bias", "gain", "center", "eps")
+
+    def __init__(self, terms, bias, gain, center, eps):
+        self.terms, self.bias, self.gain, self.center, self.eps = terms, bias, gain, center, eps
+
+
+def _terms(delta):
+    return delta.terms if isinstance(delta, WeightedSum) else [(delta, 1.0)]
+
+
+def _owed_normed(norm, delta, bias, center: bool):
+    if delta is None:
+        return None
+    return PostNormed(_terms(delta), bias, norm.gain, center, norm.eps)
+
+
+def _general_add_norm(h, delta, gain, center: bool, eps: float, out, rows, write_h: bool):
+    """h += delta in any of its forms (a tensor, partials, a weighted sum, a normed result); out = norm(h) * gain."""
+    if delta is None:
+        terms, bias, post_gain, post_center, post_eps = [], None, None, False, 0.0
+    elif isinstance(delta, PostNormed):
+        terms, bias, post_gain, post_center, post_eps = delta.terms, delta.bias, delta.gain, delta.center, delta.eps
+    else:
+        terms, bias, post_gain, post_center, post_eps = _terms(delta), None, None, False, 0.0
+    kernels.post_norm_add_norm(h, terms, bias, post_gain, post_center, post_eps, gain, center, eps, out, rows=rows,
+                               write_h=write_h)
+
+
+@register_norm("layer_norm")
+class LayerNorm:
+    """(x - mean) / sqrt(variance + eps) * gain, the variance the mean of the squared deviations; no bias."""
+
+    center = True
+
+    def __init__(self, spec, weights: dict, rt):
+        self.size, self.eps, self.rt = spec["size"], float(spec["eps"]), rt
+        self.gain = weights[spec.tensors["gain"].name].to(torch.float32).contiguous()
+
+    def libraries(self) -> set:
+        return {"post_norm"}
+
+    def owed(self, delta, bias=None):
+        """The sublayer's result ``delta`` (None: nothing), to be normed by this norm before it joins the stream."""
+        return _owed_normed(self, delta, bias, self.center)
+
+    def add(self, h, delta) -> None:
+        if delta is not None:
+            _general_add_norm(h, delta, None, False, 0.0, None, None, True)
+
+    def add_forward(self, h, delta, rows=None, write_h=True, out_dtype=None, row_scales_ok=False):
+        n = h.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, self.size), dtype=out_dtype or self.rt.act_dtype, device=h.device)
+        _general_add_norm(h, delta, self.gain, self.center, self.eps, out, rows, write_h)
+        return out
+
+
 @register_norm("rms_norm")
 class RMSNorm:
     def __init__(self, spec, weights: dict, rt):
@@ -46,10 +122,13 @@ class RMSNorm:
     def libraries(self) -> set:
         return {"elementwise", "stream_mix"}
 
-    def owed(self, delta, n_streams: int):
-        """The update by which a sublayer's result ``delta`` (None: nothing) joins ``n_streams`` copies."""
+    def owed(self, delta, n_streams: int = 0, bias=None):
+        """The update by which a sublayer's result ``delta`` (None: nothing) joins ``n_streams`` copies; without
+        ``n_streams``: the result normed by this norm before it joins the one stream (a norm behind a sublayer)."""
         if delta is None:
             return None
+        if not n_streams:
+            return _owed_normed(self, delta, bias, False)
         if self.mix is None:        # no connection weights: every copy keeps itself and gets mult * delta
             if n_streams not in self._plain:
                 self._plain[n_streams] = (torch.eye(n_streams, dtype=torch.float32, device=self.gain.device).contiguous(),
@@ -74,6 +153,9 @@ class RMSNorm:
 
     def add(self, h, delta) -> None:
         """h += delta (``delta`` [T,d] or split partials [S,T,d], added in order); nothing is normed."""
+        if isinstance(delta, (PostNormed, WeightedSum)):
+            kernels._library("post_norm")
+            return _general_add_norm(h, delta, None, False, 0.0, None, None, True)
         if h.dim() == 2 and isinstance(delta, StreamUpdate):
             h = h.unsqueeze(0)       # one copy, with connection weights of its own
         if h.dim() == 3:
@@ -85,6 +167,11 @@ class RMSNorm:
     def add_forward(self, h, delta, rows=None, write_h=True, out_dtype=None, row_scales_ok=False):
         """With ``row_scales_ok`` the caller's next products apply the norm's scale themselves; for a step of
         few tokens the result is then ``RowScaled`` (the norm in two halves, see ``parts.row_scaled``)."""
+        if isinstance(delta, (PostNormed, WeightedSum)):
+            n = h.shape[0] if rows is None else rows.numel()
+            out = torch.empty((n, self.size), dtype=out_dtype or self.rt.act_dtype, device=h.device)
+            _general_add_norm(h, delta, self.gain, False, self.eps, out, rows, write_h)
+            return out
         if h.dim() == 2 and isinstance(delta, StreamUpdate):
             h = h.unsqueeze(0)       # one copy, with connection weights of its own
         if h.dim() == 3:
