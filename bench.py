@@ -7,6 +7,7 @@ B200.  A "step" is one decode step of a batch of 8 sequences from depth 2048
     python bench.py --cpu-baseline      # the plain implementation of tests/ on the CPU, tiny configurations
     python bench.py --design tifapel    # the Tifapel decoder beside the dense decoder at equal layer sizes
     python bench.py --design voserax    # the Voserax decoder beside the Tifapel decoder's attention layers, two sizes
+    python bench.py --design ninenex    # the Ninenex decoder beside the Tifapel decoder's retention and attention layers, two sizes
 
 ``value`` is device-timed (CUDA events around K steps queued back to back);
 ``e2e`` is the same metric through ``Session.generate`` with host token ids in
@@ -195,7 +196,7 @@ def main() -> int:
                          "one replayed decode step, when each kernel's dependency resolved")
     ap.add_argument("--cpu-baseline", action="store_true",
                     help="instead of the benchmark: time the plain implementation of tests/ on the CPU (tiny configurations)")
-    ap.add_argument("--design", choices=["tifapel", "voserax"], default=None,
+    ap.add_argument("--design", choices=["tifapel", "voserax", "ninenex"], default=None,
                     help="instead of the benchmark: prefill and decode rates of that design at layer sizes of a real "
                          "model (random weights), beside the dense Qwen3 decoder at equal sizes, with every kernel's "
                          "time per step (one JSON line of its own; the default workload is untouched)")
@@ -430,6 +431,30 @@ def voserax_layers(n_layers, width, heads, kv_heads, dim, window, experts, top, 
             for i in range(n_layers)]
 
 
+def ninenex_layers(n_layers, heads, kv_heads, dim, chunk, experts, top, ff):
+    """Layers in the order mLSTM (routed experts with a shared expert), attention beside retention (dense tanh-GELU
+    feed-forward with biases), mLSTM on the first layer's weights, attention beside retention with routed experts."""
+    moe = dict(kind="moe", expert=dict(ff=ff), router=dict(experts=experts, top=top), shared=dict(ff=ff))
+    mlstm = dict(type="mlstm", mixer=dict(heads=heads, dim=dim, vdim=dim, gate_cap=15.0), mlp=moe)
+    half = max(1, heads // 2)
+    decay = [1.0 - 2.0 ** -(3 + 7 * h / max(1, half - 1)) for h in range(half)]
+    par = dict(type="parallel", mixer=dict(
+        left=dict(heads=half, kv_heads=max(1, kv_heads // 2), dim=dim, vdim=dim, scale=dim ** -0.5, mask=dict(size=chunk),
+                  rot=dict(dims=dim // 2, base=1000000.0)),
+        right=dict(heads=half, dim=dim, vdim=dim, decay=decay), left_scale=0.8, right_scale=0.5))
+    out = []
+    for i in range(n_layers):
+        kind = i % 4
+        if kind == 0:
+            out.append(json.loads(json.dumps(mlstm)))
+        elif kind == 2:
+            out.append(dict(json.loads(json.dumps(mlstm)), weights_of=i - 2))
+        else:
+            out.append(dict(json.loads(json.dumps(par)),
+                            mlp=dict(kind="dense", ff=(top + 1) * ff) if kind == 1 else json.loads(json.dumps(moe))))
+    return out
+
+
 def design_bench(args) -> int:
     """``--design tifapel``: prefill and decode rates of the Tifapel decoder at layer sizes that resemble a real model's (width 2048,
     16 heads of 128 on 4 key/value heads, a window of 1024 that keeps 4 tokens, 16 experts of 1024 of which a
@@ -441,7 +466,12 @@ def design_bench(args) -> int:
     ``--design voserax``: the same measurement of the Voserax decoder (four streams, a 4-tap convolution, a sink,
     mixed values, experts with identity and shared experts) at two sizes (width 2048 with 16 heads of 128 and 16
     experts of 1024; width 1024 with 16 heads of 64 and 8 experts of 512), beside the closest model of this package at
-    equal sizes: the Tifapel decoder's attention layers with routed experts."""
+    equal sizes: the Tifapel decoder's attention layers with routed experts.
+
+    ``--design ninenex``: the same measurement of the Ninenex decoder (mLSTM layers, layers with chunked attention
+    beside retention, a norm before and behind every sublayer, dense feed-forwards with biases, routed experts with
+    a shared expert) at the same two sizes, beside the Tifapel decoder with retention and windowed-attention layers
+    in turn (every mixer with all the heads) and routed experts."""
     import numpy as np
     import torch
 
@@ -471,6 +501,29 @@ def design_bench(args) -> int:
             runs.append(dict(sizes=dict(width=width, heads=heads, kv_heads=kv, head_dim=dim, window=window, experts=E, top=top,
                                         expert_ff=ff, shared_ff=ff, streams=4, conv=4, vocab=vocab), **res))
         print(json.dumps(dict(design="voserax", unit="tokens/s", dtype="bf16", layers=L, peaks=pk_src, hbm_gbs=pk["hbm_gbs"],
+                              bf16_tflops=pk["bf16_tflops"], data="synthetic: seeded uniform token ids, random weights",
+                              runs=runs)))
+        return 0
+    if args.design == "ninenex":
+        runs = []
+        for width, heads, kv, dim, window, E, top, ff in ((2048, 16, 4, 128, 1024, 16, 2, 1024),
+                                                          (1024, 16, 8, 64, 512, 8, 2, 512)):
+            moe = dict(kind="moe", expert=dict(ff=ff), router=dict(experts=E, top=top, scale=1.0))
+            decay = [1.0 - 2.0 ** -(3 + 7 * h / max(1, heads - 1)) for h in range(heads)]
+            ret = dict(type="retention", mlp=moe, mixer=dict(heads=heads, dim=dim, vdim=dim, decay=decay))
+            att = dict(type="attention", mlp=moe, mixer=dict(heads=heads, kv_heads=kv, dim=dim, vdim=dim, scale=dim ** -0.5,
+                                                             mask=dict(size=window, keep_first=0)))
+            models = {
+                "ninenex": dict(architecture="Ninenex", vocab=vocab, width=width, norm=dict(eps=1e-6),
+                                embedding=dict(scale=1.0), logit_scale=1.0,
+                                layers=ninenex_layers(L, heads, kv, dim, window, E, top, ff)),
+                "tifapel": dict(architecture="Tifapel", vocab=vocab, width=width, norm=dict(eps=1e-6),
+                                layers=[json.loads(json.dumps(att if i % 2 else ret)) for i in range(L)]),
+            }
+            res = _design_models(args, models, vocab, T, B, depth, rng)
+            runs.append(dict(sizes=dict(width=width, heads=heads, kv_heads=kv, head_dim=dim, chunk=window, experts=E, top=top,
+                                        expert_ff=ff, shared_ff=ff, dense_ff=(top + 1) * ff, vocab=vocab), **res))
+        print(json.dumps(dict(design="ninenex", unit="tokens/s", dtype="bf16", layers=L, peaks=pk_src, hbm_gbs=pk["hbm_gbs"],
                               bf16_tflops=pk["bf16_tflops"], data="synthetic: seeded uniform token ids, random weights",
                               runs=runs)))
         return 0

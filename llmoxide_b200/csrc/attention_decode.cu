@@ -120,8 +120,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ seq_past,
                         float* __restrict__ ws, unsigned int* __restrict__ counters, bf16* __restrict__ out, int H,
-                        int G, int window, int keep_first, float scale_log2, float sink, int n_chunks,
-                        int cluster_merge) {
+                        int G, int window, int keep_first, int mask_chunk, float scale_log2, float sink,
+                        int n_chunks, int cluster_merge) {
   using S = DecSmem<D>;
   constexpr int KSTEPS = D / 16;
   constexpr uint32_t TILE_BYTES = 2u * DEC_TILE * D * 2u;        // what one stage's copies bring
@@ -139,7 +139,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   const int n_heads = min(DEC_ROWS, R - hg * DEC_ROWS);
 
   const int p = seq_past[b];                                      // position of the new token
-  const int first = (window > 0 && p - (window - 1) > 0) ? p - (window - 1) : 0;
+  int first = (window > 0 && p - (window - 1) > 0) ? p - (window - 1) : 0;
+  if (mask_chunk > 0) first = max(first, p - p % mask_chunk);    // a chunked mask: the keys of the token's own chunk
   const int* pages = block_table + (size_t)b * table_width;
 
   uint8_t* wsm = smem + warp * S::WARP;
@@ -514,7 +515,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 template <int D>
 static int launch_decode(const void* q, void* out, const void* k_cache, const void* v_cache, long long n_pages,
                          const int* block_table, int table_width, const int* seq_past, float* ws, unsigned int* counters, int B, int H, int G,
-                         int window, int keep_first, float scale, float sink, int n_chunks, cudaStream_t stream) {
+                         int window, int keep_first, int mask_chunk, float scale, float sink, int n_chunks,
+                         cudaStream_t stream) {
   const int R = H / G;
   const int head_groups = (R + DEC_ROWS - 1) / DEC_ROWS;
   dim3 grid(n_chunks, G * head_groups, B);
@@ -542,11 +544,12 @@ static int launch_decode(const void* q, void* out, const void* k_cache, const vo
   if (cluster_merge)
     launch_pdl_cluster(kernel, grid, dim3(DEC_WARPS * 32), smem, stream, (unsigned)n_chunks, mk, mv, (const bf16*)q,
                        (const bf16*)k_cache, (const bf16*)v_cache, block_table, table_width, seq_past, ws, counters,
-                       (bf16*)out, H, G, window, keep_first, scale * 1.4426950408889634f, sink, n_chunks, cluster_merge);
+                       (bf16*)out, H, G, window, keep_first, mask_chunk, scale * 1.4426950408889634f, sink, n_chunks,
+                       cluster_merge);
   else
     launch_pdl(kernel, grid, dim3(DEC_WARPS * 32), smem, stream, mk, mv, (const bf16*)q, (const bf16*)k_cache,
                (const bf16*)v_cache, block_table, table_width, seq_past, ws, counters, (bf16*)out, H, G, window,
-               keep_first, scale * 1.4426950408889634f, sink, n_chunks, cluster_merge);
+               keep_first, mask_chunk, scale * 1.4426950408889634f, sink, n_chunks, cluster_merge);
   return LLMX_LAUNCH_STATUS();
 }
 
@@ -557,13 +560,17 @@ static int launch_decode(const void* q, void* out, const void* k_cache, const vo
 // launch (each launch leaves them zero).
 // keep_first: under a window, the sequence's first keep_first keys stay visible.
 // sink: added to the softmax's denominator (as many keys of score 0 that have no value); 0 for none.
-LLMX_API int llmx_attention_decode_sink(const void* q, void* out, const void* k_cache, const void* v_cache,
-                                        long long n_pages, const int* block_table, int table_width, const int* seq_past,
-                                        float* ws, unsigned int* counters, int B, int H, int G, int D, int window,
-                                        int keep_first, float scale, float sink, int n_chunks, cudaStream_t stream) {
+// mask_chunk n > 0: positions are cut into chunks of n, counted from the sequence's position 0, and the token sees
+// only the keys of its own chunk (beside a window: the later of the two starts; no kept first keys then).
+LLMX_API int llmx_attention_decode_masked(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                          long long n_pages, const int* block_table, int table_width,
+                                          const int* seq_past, float* ws, unsigned int* counters, int B, int H, int G,
+                                          int D, int window, int keep_first, int mask_chunk, float scale, float sink,
+                                          int n_chunks, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (!(sink >= 0.f)) return LLMX_REFUSED(1);
   if (window <= 0) keep_first = 0;
+  if (mask_chunk < 0 || (mask_chunk > 0 && keep_first > 0)) return LLMX_REFUSED(1);
   if (H <= 0 || G <= 0 || H % G || window < 0 || keep_first < 0 || n_chunks < 1 || n_chunks > DEC_MAX_CHUNKS ||
       (n_chunks > 8 && (!ws || !counters || ((uintptr_t)ws & 15))) || n_pages <= 0 ||
       ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)q & 3))
@@ -572,13 +579,21 @@ LLMX_API int llmx_attention_decode_sink(const void* q, void* out, const void* k_
 #define CASE(DD)                                                                                               \
   case DD:                                                                                                     \
     return launch_decode<DD>(q, out, k_cache, v_cache, n_pages, block_table, table_width, seq_past, ws, counters, \
-                             B, H, G, window, keep_first, scale, sink, n_chunks, stream)
+                             B, H, G, window, keep_first, mask_chunk, scale, sink, n_chunks, stream)
   switch (D) {
     CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
     CASE(144); CASE(160); CASE(176); CASE(192); CASE(208); CASE(224); CASE(240); CASE(256);
     default: return LLMX_REFUSED(1);
   }
 #undef CASE
+}
+
+LLMX_API int llmx_attention_decode_sink(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                        long long n_pages, const int* block_table, int table_width, const int* seq_past,
+                                        float* ws, unsigned int* counters, int B, int H, int G, int D, int window,
+                                        int keep_first, float scale, float sink, int n_chunks, cudaStream_t stream) {
+  return llmx_attention_decode_masked(q, out, k_cache, v_cache, n_pages, block_table, table_width, seq_past, ws, counters,
+                                      B, H, G, D, window, keep_first, 0, scale, sink, n_chunks, stream);
 }
 
 LLMX_API int llmx_attention_decode_keep(const void* q, void* out, const void* k_cache, const void* v_cache,

@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(PF_THREADS)
 attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ k_cache,
                          const bf16* __restrict__ v_cache, const int* __restrict__ block_table, int table_width,
                          const int* __restrict__ seq_start, const int* __restrict__ seq_past, int H, int G,
-                         int window, int keep_first, float scale_log2, float sink) {
+                         int window, int keep_first, int mask_chunk, float scale_log2, float sink) {
   constexpr int CHUNKS = D / 8;              // 16-byte chunks per row
   constexpr int KSTEPS = D / 16;             // k-steps of the score product
   constexpr int TILE_BYTES = PF_BK * D * 2;
@@ -81,7 +81,9 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, con
   const int past = seq_past[b];
   const int rows_here = min(PF_BQ, n_new - i0);
   const int pos_lo = past + i0, pos_hi = past + i0 + rows_here - 1;   // positions of the tile's queries
-  const int first_lo = (window > 0 && pos_lo - (window - 1) > 0) ? pos_lo - (window - 1) : 0;
+  int first_lo = (window > 0 && pos_lo - (window - 1) > 0) ? pos_lo - (window - 1) : 0;
+  // a chunked mask: a query sees the keys of its own chunk of mask_chunk positions, counted from position 0
+  if (mask_chunk > 0) first_lo = max(first_lo, pos_lo - pos_lo % mask_chunk);
   const int page_first = first_lo / PF_BK, page_last = pos_hi / PF_BK;
   // pages that hold kept first keys and lie wholly before the window's first page are walked first
   const int n_kept_tiles = keep_first > 0 ? min(page_first, (keep_first + PF_BK - 1) / PF_BK) : 0;
@@ -118,8 +120,12 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, con
 
   const int row0 = warp * 16 + (lane >> 2);
   const int p0 = past + i0 + row0, p1 = p0 + 8;                    // positions of this thread's two rows
-  const int f0 = (window > 0 && p0 - (window - 1) > 0) ? p0 - (window - 1) : 0;
-  const int f1 = (window > 0 && p1 - (window - 1) > 0) ? p1 - (window - 1) : 0;
+  int f0 = (window > 0 && p0 - (window - 1) > 0) ? p0 - (window - 1) : 0;
+  int f1 = (window > 0 && p1 - (window - 1) > 0) ? p1 - (window - 1) : 0;
+  if (mask_chunk > 0) {
+    f0 = max(f0, p0 - p0 % mask_chunk);
+    f1 = max(f1, p1 - p1 % mask_chunk);
+  }
 
   for (int t = 0; t < n_tiles; ++t) {
     const int stage = t & 1;
@@ -257,7 +263,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, con
 template <int D>
 static int launch_prefill(const void* q, void* out, const void* k_cache, const void* v_cache, const int* block_table,
                           int table_width, const int* seq_start, const int* seq_past, int B, int max_new, int H,
-                          int G, int window, int keep_first, float scale, float sink, cudaStream_t stream) {
+                          int G, int window, int keep_first, int mask_chunk, float scale, float sink,
+                          cudaStream_t stream) {
   const size_t smem = (size_t)PF_BQ * D * 2 + 4 * (size_t)PF_BK * D * 2;
   auto kernel = attention_prefill_kernel<D>;
   static bool attr_set = false;
@@ -269,26 +276,38 @@ static int launch_prefill(const void* q, void* out, const void* k_cache, const v
   dim3 grid(H, (max_new + PF_BQ - 1) / PF_BQ, B);
   launch_pdl(kernel, grid, dim3(PF_THREADS), smem, stream, (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
                                              block_table, table_width, seq_start, seq_past, H, G, window,
-                                             keep_first, scale * 1.4426950408889634f, sink);
+                                             keep_first, mask_chunk, scale * 1.4426950408889634f, sink);
   return LLMX_LAUNCH_STATUS();
 }
 
 // q, out: bf16 [T, H*D], tokens packed sequence after sequence; seq_start [B+1] offsets into the packed
 // tokens; seq_past[b] = position of sequence b's first new token; max_new = most new tokens of a sequence.
 // Head sizes 64 and 128; other sizes are refused (the general kernel takes them).
-LLMX_API int llmx_attention_prefill(const void* q, void* out, const void* k_cache, const void* v_cache,
-                                    const int* block_table, int table_width, const int* seq_start,
-                                    const int* seq_past, int B, int max_new, int H, int G, int D, int window,
-                                    int keep_first, float scale, float sink, cudaStream_t stream) {
+// mask_chunk n > 0: a query sees only the keys of its own chunk of n positions, counted from the sequence's
+// position 0 (no kept first keys then).
+LLMX_API int llmx_attention_prefill_masked(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                           const int* block_table, int table_width, const int* seq_start,
+                                           const int* seq_past, int B, int max_new, int H, int G, int D, int window,
+                                           int keep_first, int mask_chunk, float scale, float sink,
+                                           cudaStream_t stream) {
   if (B <= 0 || max_new <= 0) return 0;
+  if (mask_chunk < 0 || (mask_chunk > 0 && window > 0 && keep_first > 0)) return LLMX_REFUSED(1);
   if (H <= 0 || G <= 0 || H % G || window < 0 || keep_first < 0 || B > 65535 ||
       (max_new + PF_BQ - 1) / PF_BQ > 65535)
     return LLMX_REFUSED(1);
   if (D == 128)
     return launch_prefill<128>(q, out, k_cache, v_cache, block_table, table_width, seq_start, seq_past, B, max_new,
-                               H, G, window, window > 0 ? keep_first : 0, scale, sink, stream);
+                               H, G, window, window > 0 ? keep_first : 0, mask_chunk, scale, sink, stream);
   if (D == 64)
     return launch_prefill<64>(q, out, k_cache, v_cache, block_table, table_width, seq_start, seq_past, B, max_new, H,
-                              G, window, window > 0 ? keep_first : 0, scale, sink, stream);
+                              G, window, window > 0 ? keep_first : 0, mask_chunk, scale, sink, stream);
   return LLMX_REFUSED(1);
+}
+
+LLMX_API int llmx_attention_prefill(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                    const int* block_table, int table_width, const int* seq_start,
+                                    const int* seq_past, int B, int max_new, int H, int G, int D, int window,
+                                    int keep_first, float scale, float sink, cudaStream_t stream) {
+  return llmx_attention_prefill_masked(q, out, k_cache, v_cache, block_table, table_width, seq_start, seq_past, B,
+                                       max_new, H, G, D, window, keep_first, 0, scale, sink, stream);
 }

@@ -60,7 +60,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
                             const int* __restrict__ block_table, int table_width, const int* __restrict__ seq_start,
                             const int* __restrict__ seq_past, int H, int G, int window, int keep_first,
-                            float scale_log2, float sink) {
+                            int mask_chunk, float scale_log2, float sink) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   pdl_launch_dependents();
   pdl_wait();
@@ -75,7 +75,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int past = seq_past[b];
   const int rows_here = min(AT_ROWS, n_new - i0);
   const int pos_lo = past + i0, pos_hi = past + i0 + rows_here - 1;
-  const int first_lo = (window > 0 && pos_lo - (window - 1) > 0) ? pos_lo - (window - 1) : 0;
+  int first_lo = (window > 0 && pos_lo - (window - 1) > 0) ? pos_lo - (window - 1) : 0;
+  // a chunked mask: a query sees the keys of its own chunk of mask_chunk positions, counted from position 0
+  if (mask_chunk > 0) first_lo = max(first_lo, pos_lo - pos_lo % mask_chunk);
   const int tile_first = first_lo / AT_KEYS, tile_last = pos_hi / AT_KEYS;
   // Under a window that keeps the sequence's first keys, the tiles that hold those and lie wholly before the
   // window's first tile are walked first: place j of the walk is tile j, or past them tile_first + (j - n_kept).
@@ -192,7 +194,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
     const int pos = past + i0 + row;                              // this row's position
-    const int first = (window > 0 && pos - (window - 1) > 0) ? pos - (window - 1) : 0;
+    int first = (window > 0 && pos - (window - 1) > 0) ? pos - (window - 1) : 0;
+    if (mask_chunk > 0) first = max(first, pos - pos % mask_chunk);
     const bool row_live = row < rows_here;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     float m_used = -INFINITY;      // the maximum the exponentials are taken against (may lag the true one)
@@ -215,7 +218,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       // Tiles that some row of this CTA sees only in part (the diagonal, a window's edge, rows past the
       // sequence's end) are masked; the others, which is most of them, skip the compares.
       const bool edge = (key0 + AT_KEYS - 1 > pos_lo) || (window > 0 && key0 < pos_hi - (window - 1)) ||
-                        (rows_here < AT_ROWS);
+                        (mask_chunk > 0 && key0 < pos_hi - pos_hi % mask_chunk) || (rows_here < AT_ROWS);
       if (edge) {
 #pragma unroll
         for (int e = 0; e < AT_KEYS; ++e) {
@@ -341,13 +344,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 // q, out: bf16 [T, H*128], tokens packed sequence after sequence; k_cache, v_cache: one cache entry
 // [n_pages, G, 64, 128]; seq_start [B+1]; seq_past[b] = position of sequence b's first new token;
 // max_new = most new tokens of a sequence.
-LLMX_API int llmx_attention_prefill_tc(const void* q, void* out, const void* k_cache, const void* v_cache,
-                                       long long n_pages, const int* block_table, int table_width,
-                                       const int* seq_start, const int* seq_past, int B, int T, int max_new, int H,
-                                       int G, int D, int window, int keep_first, float scale, float sink,
-                                       cudaStream_t stream) {
+// mask_chunk n > 0: a query sees only the keys of its own chunk of n positions, counted from the sequence's
+// position 0 (no kept first keys then).
+LLMX_API int llmx_attention_prefill_tc_masked(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                              long long n_pages, const int* block_table, int table_width,
+                                              const int* seq_start, const int* seq_past, int B, int T, int max_new,
+                                              int H, int G, int D, int window, int keep_first, int mask_chunk,
+                                              float scale, float sink, cudaStream_t stream) {
   if (B <= 0 || max_new <= 0 || T <= 0) return 0;
   if (window <= 0) keep_first = 0;
+  if (mask_chunk < 0 || (mask_chunk > 0 && keep_first > 0)) return LLMX_REFUSED(1);
   if (D != AT_D || H <= 0 || G <= 0 || H % G || window < 0 || keep_first < 0 || B > 65535 || (max_new + AT_ROWS - 1) / AT_ROWS > 65535 || n_pages <= 0)
     return LLMX_REFUSED(1);
   if (((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15)) return LLMX_REFUSED(1);
@@ -370,8 +376,17 @@ LLMX_API int llmx_attention_prefill_tc(const void* q, void* out, const void* k_c
   }
   dim3 grid(H, (max_new + AT_ROWS - 1) / AT_ROWS, B);
   launch_pdl(attention_prefill_tc_kernel, grid, dim3(AT_THREADS), smem, stream, mq, mk, mv, (bf16*)out, block_table,
-             table_width, seq_start, seq_past, H, G, window, keep_first, scale * 1.4426950408889634f, sink);
+             table_width, seq_start, seq_past, H, G, window, keep_first, mask_chunk, scale * 1.4426950408889634f, sink);
   return LLMX_LAUNCH_STATUS();
+}
+
+LLMX_API int llmx_attention_prefill_tc(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                       long long n_pages, const int* block_table, int table_width,
+                                       const int* seq_start, const int* seq_past, int B, int T, int max_new, int H,
+                                       int G, int D, int window, int keep_first, float scale, float sink,
+                                       cudaStream_t stream) {
+  return llmx_attention_prefill_tc_masked(q, out, k_cache, v_cache, n_pages, block_table, table_width, seq_start,
+                                          seq_past, B, T, max_new, H, G, D, window, keep_first, 0, scale, sink, stream);
 }
 
 LLMX_API int llmx_attention_prefill_tc_status(int reset) {

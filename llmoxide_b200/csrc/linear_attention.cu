@@ -317,6 +317,7 @@ gate_scan_kernel(const TIN* __restrict__ proj, int n_split, size_t split_stride,
   const float bi = bias_i ? bias_i[h] : 0.f, bf = bias_f ? bias_f[h] : 0.f;
   pdl_wait();
   float m = *m_ptr, cum = 0.f, m_base = m;
+  int in_seg = 0;                                    // (base + j) % seg_len, kept by counting
   for (int base = 0; base < n_new; base += 32) {
     const int n = min(32, n_new - base);
     float il = 0.f, fl = 0.f;
@@ -329,13 +330,22 @@ gate_scan_kernel(const TIN* __restrict__ proj, int n_split, size_t split_stride,
       fl = fminf(zf, 0.f) - log1pf(expf(-fabsf(zf)));           // log sigmoid(zf)
     }
     float my_prev = 0.f, my_m = 0.f, my_sum = 0.f;
-    for (int j = 0; j < n; ++j) {
+    // every lane walks the chain m -> max(f + m, i); a whole block of 32 tokens is unrolled, so that the broadcasts
+    // run ahead of the chain
+    auto token = [&](int j) {
       const float f = __shfl_sync(0xffffffffu, fl, j), i = __shfl_sync(0xffffffffu, il, j);
-      if ((base + j) % seg_len == 0) cum = 0.f, m_base = m;
+      if (in_seg == 0) cum = 0.f, m_base = m;
+      if (++in_seg == seg_len) in_seg = 0;
       const float m_new = fmaxf(f + m, i);
       cum += f;
       if (lane == j) my_prev = m, my_m = m_new, my_sum = cum + m_base;
       m = m_new;
+    };
+    if (n == 32) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) token(j);
+    } else {
+      for (int j = 0; j < n; ++j) token(j);
     }
     if (lane < n)
       *reinterpret_cast<float4*>(gates + ((size_t)(t0 + base + lane) * H + h) * 4) =

@@ -340,7 +340,7 @@ class Engine:
         """What the reference's ``Info`` carries (llmoxide/src/backend.rs:36-49)."""
         return dict(architecture=self.spec.architecture, dtype=self.options.dtype, device=str(self.device),
                     vocab_size=self.spec.vocab_size, hidden_size=self.spec.hidden_size,
-                    n_layers=len(self.spec.blocks), stop_ids=tuple(self.spec.stop_ids),
+                    n_layers=len(self.spec.schedule), stop_ids=tuple(self.spec.stop_ids),
                     max_tokens=self.cache.n_pages * PAGE, max_batch=self.cache.n_slots,
                     max_seq_len=self.cache.alloc.max_seq_len, cache_bytes=self.cache.bytes(),
                     summary=self.config.summary() if hasattr(self.config, "summary") else "")

@@ -584,11 +584,12 @@ def _counters(device, n: int):
 
 def attention_decode(q, out, k_cache, v_cache, block_table, seq_past, n_heads: int, n_kv_heads: int,
                      head_dim: int, window, scale: float, n_chunks: int = 0, keep_first: int = 0,
-                     sink: float = 0.0) -> None:
+                     sink: float = 0.0, chunk: int = 0) -> None:
     """One new token per sequence, bfloat16: q, out [B,H*D] in batch order;
     seq_past[b] is the token's position.  Each sequence's keys are split over
     n_chunks CTAs (0: chosen from the batch's shape), which merge inside a
-    cluster, or beyond 8 chunks through a float32 workspace."""
+    cluster, or beyond 8 chunks through a float32 workspace.  ``chunk`` n > 0 is
+    the chunked mask of ``attention_paged`` (nothing to do with n_chunks)."""
     _dev(q, out, k_cache, v_cache, block_table, seq_past)
     _contig("q", q), _contig("out", out), _contig("block_table", block_table)
     assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
@@ -598,6 +599,8 @@ def attention_decode(q, out, k_cache, v_cache, block_table, seq_past, n_heads: i
     n_pages = block_table.shape[1]
     if window:
         n_pages = min(n_pages, (window + PAGE - 2) // PAGE + 1 + (int(keep_first or 0) + PAGE - 1) // PAGE)
+    if chunk:
+        n_pages = min(n_pages, (int(chunk) + PAGE - 1) // PAGE + 1)
     group = n_heads // n_kv_heads
     n_chunks = n_chunks or decode_chunks(B, n_kv_heads, group, n_pages, n_sm(q.device))
     ws = counters = None
@@ -605,13 +608,13 @@ def attention_decode(q, out, k_cache, v_cache, block_table, seq_past, n_heads: i
         ws = guard.scratch((B * n_heads * n_chunks * (head_dim + 4),), torch.float32, q.device,
                            "decode attention workspace")
         counters = _counters(q.device, B * n_kv_heads * ((group + 7) // 8))
-    f = _fn("attention_decode", "llmx_attention_decode_sink",
+    f = _fn("attention_decode", "llmx_attention_decode_masked",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-             c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p])
     _check(f(_ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(block_table),
              block_table.shape[1],
              _ptr(seq_past), _ptr(ws), _ptr(counters), B, n_heads, n_kv_heads, head_dim, int(window or 0),
-             int(keep_first or 0), scale, float(sink or 0.0), n_chunks, _stream()), "attention_decode")
+             int(keep_first or 0), int(chunk or 0), scale, float(sink or 0.0), n_chunks, _stream()), "attention_decode")
 
 
 def attention_decode_status() -> int:
@@ -627,38 +630,40 @@ def attention_prefill_supports(q, k_cache, head_dim: int) -> bool:
 
 def attention_prefill(q, out, k_cache, v_cache, block_table, seq_start, seq_past, n_seqs: int, max_new: int,
                       n_heads: int, n_kv_heads: int, head_dim: int, window, scale: float, keep_first: int = 0,
-                      sink: float = 0.0) -> None:
+                      sink: float = 0.0, chunk: int = 0) -> None:
     """Prompt attention on the tensor cores, bfloat16, head sizes 64 and 128:
-    q, out [T,H*D] packed sequence after sequence.  Under a window the first ``keep_first`` keys stay visible."""
+    q, out [T,H*D] packed sequence after sequence.  Under a window the first ``keep_first`` keys stay visible;
+    ``chunk`` n > 0 is the chunked mask of ``attention_paged``."""
     _dev(q, out, k_cache, v_cache, block_table, seq_start, seq_past)
     _contig("q", q), _contig("out", out), _contig("block_table", block_table)
     if not attention_prefill_supports(q, k_cache, head_dim):
         raise Unsupported(f"the tiled prompt attention takes bfloat16 and head sizes 64 or 128, not {head_dim}")
-    f = _fn("attention_prefill", "llmx_attention_prefill",
+    f = _fn("attention_prefill", "llmx_attention_prefill_masked",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
-             c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
     _check(f(_ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
              _ptr(seq_start), _ptr(seq_past), n_seqs, max_new, n_heads, n_kv_heads, head_dim, int(window or 0),
-             int(keep_first or 0), scale, float(sink or 0.0), _stream()), "attention_prefill")
+             int(keep_first or 0), int(chunk or 0), scale, float(sink or 0.0), _stream()), "attention_prefill")
 
 
 def attention_prefill_tc(q, out, k_cache, v_cache, block_table, seq_start, seq_past, n_seqs: int, max_new: int,
                          n_heads: int, n_kv_heads: int, head_dim: int, window, scale: float, keep_first: int = 0,
-                         sink: float = 0.0) -> None:
+                         sink: float = 0.0, chunk: int = 0) -> None:
     """Prompt attention on tcgen05, bfloat16, head size 128: q, out [T,H*128]
-    packed sequence after sequence; the cache entry is [n_pages,G,64,128]."""
+    packed sequence after sequence; the cache entry is [n_pages,G,64,128].  ``chunk`` n > 0 is the chunked mask
+    of ``attention_paged``."""
     _dev(q, out, k_cache, v_cache, block_table, seq_start, seq_past)
     _contig("q", q), _contig("out", out), _contig("block_table", block_table)
     assert k_cache.is_contiguous() and v_cache.is_contiguous()
     if head_dim != 128 or q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
         raise Unsupported("the tcgen05 prompt attention takes bfloat16 and head size 128")
-    f = _fn("attention_prefill_tc", "llmx_attention_prefill_tc",
+    f = _fn("attention_prefill_tc", "llmx_attention_prefill_tc_masked",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
-             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
     _check(f(_ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(block_table),
              block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs, q.shape[0], max_new, n_heads,
-             n_kv_heads, head_dim, int(window or 0), int(keep_first or 0), scale, float(sink or 0.0), _stream()),
-           "attention_prefill_tc")
+             n_kv_heads, head_dim, int(window or 0), int(keep_first or 0), int(chunk or 0), scale, float(sink or 0.0),
+             _stream()), "attention_prefill_tc")
 
 
 def attention_prefill_tc_status(reset: bool = True) -> int:

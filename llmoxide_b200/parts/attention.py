@@ -70,7 +70,7 @@ class GQAttention:
         if self.H % self.G:
             raise Unsupported(f"{self.H} heads are not a multiple of {self.G} kv heads")
         # the shape the tiled kernels are written for; every other one goes to the general kernel
-        self.plain = self.Dv == self.D and self.D % 16 == 0 and not self.chunk
+        self.plain = self.Dv == self.D and self.D % 16 == 0
         if max(self.D, self.Dv) > 256:
             raise Unsupported(f"head sizes {self.D}/{self.Dv}: the attention kernels take sizes up to 256")
         t = spec.tensors
@@ -197,21 +197,21 @@ class GQAttention:
         for prompts the tcgen05 kernel at head size 128 and the mma.sync tiled
         kernel at head size 64; the general kernel otherwise (values of another
         size than the keys among them) and always in float32.  All of them take
-        a window that keeps its first keys."""
+        a window that keeps its first keys, and a chunked mask."""
         H, G, D = self.H, self.G, self.D
         fast = (self.plain and q.dtype == torch.bfloat16 and view.k.dtype == torch.bfloat16
                 and self.rt.tensor_cores and self.scale > 0)       # (the tiled kernels take the maximum before the scale)
         if fast and ctx.is_decode:
             kernels.attention_decode(q, out, view.k, view.v, block_table, ctx.seq_past, H, G, D, self.window,
-                                     self.scale, keep_first=self.keep_first, sink=self.sink)
+                                     self.scale, keep_first=self.keep_first, sink=self.sink, chunk=self.chunk)
         elif fast and D == 128:
             kernels.attention_prefill_tc(q, out, view.k, view.v, block_table, ctx.seq_start, ctx.seq_past,
                                          ctx.n_seqs, ctx.max_new, H, G, D, self.window, self.scale,
-                                         keep_first=self.keep_first, sink=self.sink)
+                                         keep_first=self.keep_first, sink=self.sink, chunk=self.chunk)
         elif fast and kernels.attention_prefill_supports(q, view.k, D):
             kernels.attention_prefill(q, out, view.k, view.v, block_table, ctx.seq_start, ctx.seq_past,
                                       ctx.n_seqs, ctx.max_new, H, G, D, self.window, self.scale,
-                                      keep_first=self.keep_first, sink=self.sink)
+                                      keep_first=self.keep_first, sink=self.sink, chunk=self.chunk)
         else:
             kernels.attention_paged(q, out, view.k, view.v, block_table, ctx.token_seq, ctx.token_pos,
                                     H, G, D, self.window, self.scale, v_head_dim=self.Dv, keep_first=self.keep_first,

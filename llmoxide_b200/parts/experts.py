@@ -126,6 +126,9 @@ class RoutedExperts:
         kernels.moe_router(x, self.router, ids, pair_w, self.n_groups, self.keep_groups, self.group_top, self.score,
                            self.normalize, self.norm_eps, self.scale, bias=self.correction, extra_out=shared_z,
                            logit_bias=self.router_bias)
+        probe = getattr(ctx, "probe", None)
+        if probe:
+            probe("router_ids", ids), probe("router_weights", pair_w)
         perm = torch.empty((P,), dtype=torch.int32, device=dev)
         fast = self.tensor_cores and x.dtype == torch.bfloat16 and kernels.moe_tc_supports(x, self.gate_up)
         rows = self.tile_rows(P) if fast else kernels.MOE_TILE

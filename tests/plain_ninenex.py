@@ -220,10 +220,18 @@ def route(z, top):
     return idx[:, :top], torch.softmax(vals[:, :top], dim=-1)
 
 
-def moe_ff(h, w, p, mlp):
+def moe_ff(h, w, p, mlp, forced=None, logits_out=None):
+    """``forced`` [T, top]: experts to use instead of the router's own choice (their weights are still the softmax
+    over their logits); ``logits_out``: a list that receives the router's logits.  Both serve comparisons with a
+    16-bit implementation, whose rounding may decide a near tie the other way."""
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
     z = linear(h, w, p + "router", bias=True)
     idx, wt = route(z, top)
+    if logits_out is not None:
+        logits_out.append(z)
+    if forced is not None:
+        idx = torch.as_tensor(forced, dtype=torch.long)
+        wt = torch.softmax(z.gather(1, idx), dim=-1)
     out = torch.zeros((h.shape[0], w[p + "e0.down"].shape[0]), dtype=F)
     for e in range(E):
         ye = expert(h, w, f"{p}e{e}.")
@@ -238,9 +246,10 @@ def moe_ff(h, w, p, mlp):
 # Model
 # --------------------------------------------------------------------------
 
-def forward(cfg, w, tokens, layers_out=None):
+def forward(cfg, w, tokens, layers_out=None, routing=None, router_logits_out=None):
     """Logits [T, vocab] of one sequence; ``layers_out``: a list that receives the residual stream after
-    every layer run."""
+    every layer run; ``routing``: {layer run: experts [T, top]} to use instead of the router's own choice;
+    ``router_logits_out``: a dict that receives {layer run: router logits [T, experts]}."""
     eps = float(cfg["norm"]["eps"])
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)] * float(cfg["embedding"]["scale"])
     for i, layer in enumerate(cfg["layers"]):
@@ -257,7 +266,13 @@ def forward(cfg, w, tokens, layers_out=None):
         mlp = layer.get("mlp")
         if mlp is not None:
             hin = layer_norm(x, w[p + "norm2"], eps)
-            y = dense_ff(hin, w, p + "mlp.") if mlp["kind"] == "dense" else moe_ff(hin, w, p + "mlp.", mlp)
+            if mlp["kind"] == "dense":
+                y = dense_ff(hin, w, p + "mlp.")
+            else:
+                zs = []
+                y = moe_ff(hin, w, p + "mlp.", mlp, forced=(routing or {}).get(i), logits_out=zs)
+                if router_logits_out is not None:
+                    router_logits_out[i] = zs[0]
             x = x + layer_norm(y, w[p + "norm2b"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())
