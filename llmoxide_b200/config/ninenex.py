@@ -115,16 +115,23 @@ class NinenexConfig:
             mlp = layer.get("mlp")
             if mlp is not None:
                 self._check_mlp(mlp, where + ".mlp")
-            src = layer.get("weights_of")
-            if src is not None:
-                if not isinstance(src, int) or isinstance(src, bool) or not (0 <= src < i):
-                    raise ConfigError(f"{where}.weights_of {src!r} must name an earlier layer")
-                other = self.layers[src]
-                if other.get("weights_of") is not None:
-                    raise ConfigError(f"{where}.weights_of {src}: that layer has no tensors of its own")
+            if layer.get("weights_of") is not None:
+                other = self.layers[self.source_of(i)]
                 for key in ("type", "mixer", "mlp"):
                     if other.get(key) != layer.get(key):
-                        raise ConfigError(f"{where}.weights_of {src}: '{key}' differs from that layer's")
+                        raise ConfigError(f"{where}.weights_of {layer['weights_of']}: '{key}' differs from that layer's")
+
+    def source_of(self, i: int) -> int:
+        """The layer whose tensors layer i uses: itself, or where its ``weights_of`` leads (a layer that borrows may
+        be named by another that borrows; the chain ends at a layer with tensors of its own)."""
+        seen = {i}
+        while self.layers[i].get("weights_of") is not None:
+            src = self.layers[i]["weights_of"]
+            if isinstance(src, bool) or not isinstance(src, int) or not 0 <= src < len(self.layers) or src in seen:
+                raise ConfigError(f"layers[{i}].weights_of {src!r} must name another layer, and not in a circle")
+            seen.add(src)
+            i = src
+        return i
 
     @staticmethod
     def _check_mlstm(m: dict, where: str) -> None:
@@ -148,8 +155,8 @@ class NinenexConfig:
         if mask is not None:
             _positive_int(_need(mask, "size", lw + ".mask"), lw + ".mask.size")
         rot = left.get("rot")
-        if rot is not None:
-            dims = _positive_int(_need(rot, "dims", lw + ".rot"), lw + ".rot.dims")
+        if rot is not None and _need(rot, "dims", lw + ".rot") != 0:
+            dims = _positive_int(rot["dims"], lw + ".rot.dims")
             if dims % 2 or dims > left["dim"]:
                 raise ConfigError(f"{lw}.rot.dims {dims} must be even and at most dim {left['dim']}")
             if not _number(_need(rot, "base", lw + ".rot"), lw + ".rot.base") > 0:
@@ -218,7 +225,7 @@ class NinenexConfig:
             hidden_size=d, n_heads=H, n_kv_heads=G, head_dim=D, v_head_dim=Dv, scale=float(left["scale"]),
             window=None, chunk=mask["size"] if mask else 0, qk_norm_eps=None, own_kv=True), lt)
         position = None
-        if rot:
+        if rot and rot["dims"]:
             position = PartSpec("rope_neox", dict(n_rot=rot["dims"], base=float(rot["base"]), angles="float32"))
         Hr, Dr, Dvr = right["heads"], right["dim"], right["vdim"]
         rp = p + "mix.right."
@@ -268,19 +275,19 @@ class NinenexConfig:
         norm = lambda name: PartSpec("layer_norm", dict(size=d, eps=eps), dict(gain=TensorSpec(name, (d,), "vector")))
         blocks, schedule, block_of = [], [], {}
         for i, layer in enumerate(self.layers):
-            src = layer.get("weights_of")
-            if src is None:
-                p = f"l{i}."
-                mixer, position = self._mixer(p, layer["type"], layer["mixer"])
-                mlp = layer.get("mlp")
-                norms = dict(mixer=norm(p + "norm1"), mixer_post=norm(p + "norm1b"))
-                if mlp is not None:
-                    norms.update(feed_forward=norm(p + "norm2"), feed_forward_post=norm(p + "norm2b"))
-                block_of[i] = len(blocks)
-                blocks.append(BlockSpec("sandwich", mixer, self._feed_forward(p, mlp), norms, position))
-                src = i
-            # a layer that borrows another's weights runs that layer's block on a cache entry of its own
-            schedule.append(LayerCall(layer=block_of[src], cache=i))
+            if layer.get("weights_of") is not None:
+                continue
+            p = f"l{i}."
+            mixer, position = self._mixer(p, layer["type"], layer["mixer"])
+            mlp = layer.get("mlp")
+            norms = dict(mixer=norm(p + "norm1"), mixer_post=norm(p + "norm1b"))
+            if mlp is not None:
+                norms.update(feed_forward=norm(p + "norm2"), feed_forward_post=norm(p + "norm2b"))
+            block_of[i] = len(blocks)
+            blocks.append(BlockSpec("sandwich", mixer, self._feed_forward(p, mlp), norms, position))
+        # a layer that borrows another's weights runs that layer's block on a cache entry of its own
+        for i in range(len(self.layers)):
+            schedule.append(LayerCall(layer=block_of[self.source_of(i)], cache=i))
         return ModelSpec(
             architecture="Ninenex", hidden_size=d, vocab_size=self.vocab,
             embedding=PartSpec("gather", dict(scale=self.embedding_scale), dict(table=TensorSpec("embed", (self.vocab, d)))),

@@ -85,7 +85,7 @@ def test_description_names_every_tensor_once_with_the_shapes_of_the_configuratio
     (lambda c: c["layers"][0]["mlp"].__setitem__("kind", "conv"), "kind"),
     (lambda c: c["layers"][2].__setitem__("weights_of", 2), "weights_of"),
     (lambda c: c["layers"][2].__setitem__("weights_of", 1), "differs"),
-    (lambda c: c["layers"][3].update(copy.deepcopy(c["layers"][2]), weights_of=2), "no tensors of its own"),
+    (lambda c: (c["layers"][0].update(weights_of=2), c["layers"][2].update(weights_of=0)), "circle"),
     (lambda c: c["layers"][2]["mixer"].__setitem__("left_scale", 1.0), "differs"),
     (lambda c: c.pop("norm"), "norm"),
     (lambda c: c.pop("logit_scale"), "logit_scale"),
@@ -97,6 +97,26 @@ def test_inconsistent_configurations_are_refused(change, word):
     with pytest.raises(ConfigError) as e:
         read_config(raw)
     assert word in str(e.value)
+
+
+def test_borrowed_weights_through_a_chain_and_from_a_later_layer():
+    """A layer may borrow from one that borrows, and from a layer further on: each runs the block of the layer the
+    chain ends at, on a cache entry of its own.  A rotation of zero dimensions is no rotation."""
+    raw = copy.deepcopy(NX_A)
+    raw["layers"][3] = dict(copy.deepcopy(raw["layers"][2]), weights_of=2)      # 3 -> 2 -> 0
+    spec = read_config(raw).to_spec()
+    assert [c.layer for c in spec.schedule] == [0, 1, 0, 0] and [c.cache for c in spec.schedule] == [0, 1, 2, 3]
+    raw = copy.deepcopy(NX_A)
+    raw["layers"][0]["weights_of"] = 2                                            # the first layer borrows the third's
+    raw["layers"][2].pop("weights_of")
+    spec = read_config(raw).to_spec()
+    assert [c.layer for c in spec.schedule] == [1, 0, 1, 2]
+    assert {t.name.split(".")[0] for t in spec.tensors()} >= {"l1", "l2", "l3"}
+    assert not any(t.name.startswith("l0.") for t in spec.tensors())
+    raw = copy.deepcopy(NX_A)
+    for i in (0, 2):
+        raw["layers"][i]["mixer"]["left"]["rot"]["dims"] = 0
+    assert read_config(raw).to_spec().blocks[0].position is None
 
 
 # ---------------------------------------------------------------------------------------------------------
