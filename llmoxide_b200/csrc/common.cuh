@@ -205,6 +205,8 @@ enum { LLMX_ACT_SILU = 0, LLMX_ACT_RELU = 1, LLMX_ACT_CLAMPED_SWISH = 2, LLMX_AC
 struct GateAct {
   int kind;
   float slope, limit, shift;
+  const float* bias;     // null, or one float32 per row of the fused gate|up matrix (padded to whole row tiles),
+                         // added before the activation; read only by the tensor-core product's gated epilogues
 };
 __device__ __forceinline__ float gated_act(const GateAct a, float g, float u) {
   if (a.kind == LLMX_ACT_SILU) return (g / (1.0f + expf(-g))) * u;

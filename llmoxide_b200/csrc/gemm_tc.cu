@@ -73,6 +73,8 @@ __device__ __forceinline__ void epilogue_tile(uint32_t acc_addr, bool have_acc, 
   const int row = quad * 32 + lane;
   const int n = MODE == 2 ? (n0 >> 1) + quad * 16 + (lane & 15) : n0 + row;
   const bool upper = lane >= 16;
+  // the bias of this thread's own row of W (MODE 2: lanes 0..15 hold gate rows, 16..31 the up rows)
+  const float own_bias = (MODE == 2 && act.bias != nullptr) ? act.bias[n0 + row] : 0.f;
 #pragma unroll 1
   for (int c = 0; c < BN; c += 16) {
     if (t0 + c >= T) break;
@@ -93,6 +95,8 @@ __device__ __forceinline__ void epilogue_tile(uint32_t acc_addr, bool have_acc, 
       }
     }
     if (MODE == 2) {
+#pragma unroll
+      for (int e = 0; e < 16; ++e) v[e] += own_bias;
 #pragma unroll
       for (int e = 0; e < 16; e += 2) {
         const float got = __shfl_xor_sync(0xffffffffu, upper ? v[e] : v[e + 1], 16);
@@ -136,6 +140,7 @@ __device__ __forceinline__ void epilogue_tile_staged(uint32_t acc_addr, const CU
   constexpr int COLS = MODE == 2 ? 64 : 128;
   const bool upper = lane >= 16;
   const int col = MODE == 2 ? quad * 16 + (lane & 15) : quad * 32 + lane;
+  const float own_bias = (MODE == 2 && act.bias != nullptr) ? act.bias[n0 + quad * 32 + lane] : 0.f;
 #pragma unroll 1
   for (int c = 0; c < BN; c += ROWS) {
     if (t0 + c >= T) break;
@@ -146,6 +151,8 @@ __device__ __forceinline__ void epilogue_tile_staged(uint32_t acc_addr, const CU
     if (first_thread) bulk_wait_read<1>();              // the store that last read this buffer is done with it
     asm volatile("bar.sync 1, 128;" ::: "memory");
     if (MODE == 2) {
+#pragma unroll
+      for (int e = 0; e < ROWS; ++e) v[e] += own_bias;
 #pragma unroll
       for (int e = 0; e < ROWS; e += 2) {
         const float got = __shfl_xor_sync(0xffffffffu, upper ? v[e] : v[e + 1], 16);
@@ -684,10 +691,16 @@ static int sm_count() {
 // The gated activation of the launches that follow from this thread (modes 1 and 2): it travels to the kernel as
 // an argument, so a launch, or a captured graph node, keeps the one that was set when it was made.  SiLU until
 // set otherwise; kinds in common.cuh.
-static thread_local GateAct t_gate_act = {LLMX_ACT_SILU, 1.f, 0.f, 0.f};
+static thread_local GateAct t_gate_act = {LLMX_ACT_SILU, 1.f, 0.f, 0.f, nullptr};
 LLMX_API int llmx_gemm_tc_gate_act(int kind, float slope, float limit, float shift) {
   if (kind < LLMX_ACT_SILU || kind > LLMX_ACT_LAST) return LLMX_REFUSED(1);
-  t_gate_act = GateAct{kind, slope, limit, shift};
+  t_gate_act = GateAct{kind, slope, limit, shift, t_gate_act.bias};
+  return 0;
+}
+// The bias of the gated launches that follow (interleaved layout only): float32, one per row of W in W's own row
+// order, padded with zeros to a multiple of 256 rows; null for none.  Added to the accumulator before the activation.
+LLMX_API int llmx_gemm_tc_gate_bias(const float* bias) {
+  t_gate_act.bias = bias;
   return 0;
 }
 

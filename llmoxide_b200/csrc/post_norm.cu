@@ -10,8 +10,9 @@
 //   out[r,:] = norm(v) * gain                         when out is given
 // Either norm is a layer norm without bias, (x - mean) / sqrt(mean((x - mean)^2) + eps), or an RMS norm,
 // x / sqrt(mean(x^2) + eps); the two norms choose independently (`post_center`, `center`).  Everything is float32;
-// mean and variance are taken in two passes over the row, which is staged in shared memory.  The thread count and
-// each thread's elements depend on d alone, so a row's sums do not depend on the batch.
+// mean and variance are taken in two passes over the row, which is held in registers (rows of up to 8192 aligned
+// floats) or staged in shared memory.  The thread count and each thread's elements depend on d (and the pointers'
+// alignment) alone, so a row's sums do not depend on the batch.
 #include "common.cuh"
 
 __device__ __forceinline__ float4 pn_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
@@ -153,6 +154,107 @@ post_norm_add_norm_kernel(float* __restrict__ h, const PnGroup g0, const PnGroup
   }
 }
 
+// The same for rows of up to 16 floats a thread (d <= 8192, everything 16-byte aligned): the row stays in registers.
+// Thread j owns the float4s j, j + T, .., j + (NV - 1) T of the row; NV and T depend on d alone (8 floats a thread
+// up to d = 4096: more of them make the block-wide sums cheaper for a prompt's rows but a decode step's few rows
+// slower).  Mean and variance are still two passes (over registers).
+template <int NV>
+__device__ __forceinline__ void pn_stats_reg(const float4 (&v)[NV], const bool (&live)[NV], int d, bool center,
+                                             float eps, float* red, float& mean, float& rstd) {
+  mean = 0.f;
+  if (center) {
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k)
+      if (live[k]) s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+    mean = block_sum(s, red) / (float)d;
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k)
+    if (live[k]) {
+      const float a = v[k].x - mean, b = v[k].y - mean, c = v[k].z - mean, e = v[k].w - mean;
+      ss += (a * a + b * b) + (c * c + e * e);
+    }
+  rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
+}
+
+template <typename TO, int NV>
+__global__ void __launch_bounds__(512)
+post_norm_add_norm_reg_kernel(float* __restrict__ h, const PnGroup g0, const PnGroup g1,
+                              const float* __restrict__ bias, const float* __restrict__ post_gain, int post_center,
+                              float post_eps, const int* __restrict__ rows, const float* __restrict__ gain, int center,
+                              float eps, TO* __restrict__ out, int d, int write_h) {
+  __shared__ float red[32];
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  const int t = rows ? rows[r] : r;                     // a step input, not a result of the kernel before
+  float* hrow = h + (size_t)t * d;
+  const int n4 = d >> 2;
+  float4 v[NV];
+  bool live[NV];
+  int col[NV];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int j = threadIdx.x + k * blockDim.x;
+    live[k] = j < n4;
+    col[k] = j * 4;
+  }
+  pdl_wait();
+  if (g0.p) {
+    const size_t at0 = (size_t)t * d;
+    float4 x[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) x[k] = live[k] ? pn_load4(hrow + col[k]) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (live[k]) {
+        y = pn_group4(g0, at0 + col[k]);
+        if (g1.p) {
+          const float4 z = pn_group4(g1, at0 + col[k]);
+          y.x += z.x, y.y += z.y, y.z += z.z, y.w += z.w;
+        }
+        if (bias) {
+          const float4 b = pn_load4(bias + col[k]);
+          y.x += b.x, y.y += b.y, y.z += b.z, y.w += b.w;
+        }
+      }
+      v[k] = y;
+    }
+    if (post_gain) {
+      float mean, rstd;
+      pn_stats_reg<NV>(v, live, d, post_center != 0, post_eps, red, mean, rstd);
+#pragma unroll
+      for (int k = 0; k < NV; ++k)
+        if (live[k]) {
+          const float4 g = pn_load4(post_gain + col[k]);
+          v[k].x = ((v[k].x - mean) * rstd) * g.x, v[k].y = ((v[k].y - mean) * rstd) * g.y;
+          v[k].z = ((v[k].z - mean) * rstd) * g.z, v[k].w = ((v[k].w - mean) * rstd) * g.w;
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      v[k] = make_float4(x[k].x + v[k].x, x[k].y + v[k].y, x[k].z + v[k].z, x[k].w + v[k].w);
+      if (write_h && live[k]) pn_store4(hrow + col[k], v[k]);
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < NV; ++k) v[k] = live[k] ? pn_load4(hrow + col[k]) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (!out) return;
+  float mean, rstd;
+  pn_stats_reg<NV>(v, live, d, center != 0, eps, red, mean, rstd);
+  TO* orow = out + (size_t)r * d;
+#pragma unroll
+  for (int k = 0; k < NV; ++k)
+    if (live[k]) {
+      const float4 g = pn_load4(gain + col[k]);
+      pn_store4(orow + col[k], make_float4(((v[k].x - mean) * rstd) * g.x, ((v[k].y - mean) * rstd) * g.y,
+                                           ((v[k].z - mean) * rstd) * g.z, ((v[k].w - mean) * rstd) * g.w));
+    }
+}
+
 // h float32 [T, d]; delta0 / delta1: null, or n_split partials [T, d] split_stride elements apart, each group
 // times its weight (delta1 only beside delta0); bias, post_gain, gain: float32 [d] or null; rows: int32 [n_rows]
 // or null (every row of h); out: [n_rows, d] or null.
@@ -189,12 +291,27 @@ LLMX_API int llmx_post_norm_add_norm(float* h, const void* delta0, int dtype0, i
     launch_pdl(post_norm_add_norm_kernel<TO, VEC>, dim3(n_rows), dim3(threads), smem, stream, h, g0, g1, bias,           \
                post_gain, post_center, post_eps, rows, gain, center, eps, (TO*)out, d, write_h);                         \
   } while (0)
-  if (out && out_dtype == LLMX_BF16) {
+  if (out && out_dtype != LLMX_BF16 && out_dtype != LLMX_F32) return LLMX_REFUSED(2);
+  const bool out_bf16 = out && out_dtype == LLMX_BF16;
+  const int n4 = d / 4;
+  if (vec && n4 <= 2048) {                              // the row in registers
+    const int nv = n4 > 1024 ? 4 : n4 > 128 ? 2 : 1;
+    const int reg_threads = ((n4 + nv - 1) / nv + 31) / 32 * 32;
+#define GO_REG(TO, NV)                                                                                                   \
+    launch_pdl(post_norm_add_norm_reg_kernel<TO, NV>, dim3(n_rows), dim3(reg_threads), 0, stream, h, g0, g1, bias,       \
+               post_gain, post_center, post_eps, rows, gain, center, eps, (TO*)out, d, write_h)
+    if (out_bf16) {
+      if (nv == 4) GO_REG(bf16, 4); else if (nv == 2) GO_REG(bf16, 2); else GO_REG(bf16, 1);
+    } else {
+      if (nv == 4) GO_REG(float, 4); else if (nv == 2) GO_REG(float, 2); else GO_REG(float, 1);
+    }
+#undef GO_REG
+    return LLMX_LAUNCH_STATUS();
+  }
+  if (out_bf16) {
     if (vec) GO(bf16, true); else GO(bf16, false);
-  } else if (!out || out_dtype == LLMX_F32) {
-    if (vec) GO(float, true); else GO(float, false);
   } else {
-    return LLMX_REFUSED(2);
+    if (vec) GO(float, true); else GO(float, false);
   }
 #undef GO
   return LLMX_LAUNCH_STATUS();

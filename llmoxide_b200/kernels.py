@@ -717,8 +717,21 @@ def _set_tc_gate_act(activation) -> None:
         _tc_gate_act[0] = key
 
 
+_tc_gate_bias = [0]               # the bias pointer the gemm_tc library was last told (0: none)
+TC_BIAS_PAD = 256                 # a gated launch's bias covers whole row tiles of a CTA pair
+
+
+def _set_tc_gate_bias(bias) -> None:
+    """The bias of the gated tensor-core launches that follow (a kernel argument, set on the host); None: none."""
+    ptr = 0 if bias is None else bias.data_ptr()
+    if _tc_gate_bias[0] != ptr:
+        f = _fn("gemm_tc", "llmx_gemm_tc_gate_bias", [c_void_p])
+        f(ptr or None)
+        _tc_gate_bias[0] = ptr
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_split: int = 1, gated=False,
-            pair: bool = False, scale=None, accumulate: bool = False, activation="silu") -> None:
+            pair: bool = False, scale=None, accumulate: bool = False, activation="silu", gate_bias=None) -> None:
     """bfloat16 x [T,K] times w [N,K]^T on tcgen05.  ``out`` is [T,N] (bfloat16
     or float32), or float32 partials [n_split,T,N] of a split reduction, or,
     with ``gated``, [T,N/2] = silu(gate) * up: ``gated=True`` (or 1) for
@@ -729,7 +742,9 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_split: int = 
     (one float32 addition per element, whatever order the tiles finish in).
     ``scale = (sumsq, parts, eps, d)``, for T <= 64: output row t is multiplied
     by 1/sqrt(sum(sumsq[:parts, t]) / d + eps) before any activation (the
-    second half of an RMSNorm whose first half is ``add_gain_sumsq``)."""
+    second half of an RMSNorm whose first half is ``add_gain_sumsq``).
+    ``gate_bias`` (``gated=2`` only): float32, one per row of w in w's row order, zero-padded to a multiple of
+    ``TC_BIAS_PAD`` rows; added to the products before the activation."""
     gated = int(gated)
     _dev(x, w, out)
     T, K = x.shape
@@ -739,6 +754,13 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_split: int = 
         if not gemm_tc_gated_supports(activation):
             raise Unsupported(f"the tensor-core product has no epilogue for the activation {activation!r}")
         _set_tc_gate_act(activation)
+        if gate_bias is not None:
+            _dev(gate_bias)
+            assert gated == 2 and gate_bias.dtype == torch.float32 and gate_bias.is_contiguous()
+            assert gate_bias.numel() >= (N + TC_BIAS_PAD - 1) // TC_BIAS_PAD * TC_BIAS_PAD
+        _set_tc_gate_bias(gate_bias)
+    else:
+        assert gate_bias is None
     if gated:
         assert n_split == 1 and out.shape == (T, N // 2)
         ldy, stride = N // 2, 0

@@ -5,8 +5,8 @@ may also be "relu", "gelu_tanh" (0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))
 ("clamped_swish", slope, limit, shift):
 min(g, limit) * sigmoid(slope * min(g, limit)) * (clamp(u, -limit, limit) + shift).
 Tensors ``gate_bias``, ``up_bias``, ``down_bias``: biases of the three projections (gate and up: added where the
-activation reads the product; down: offered as ``out_bias`` to an arrangement that adds it in its norm kernel,
-else added here)."""
+activation reads the product, which is the tensor-core product's own epilogue where that applies the activation;
+down: offered as ``out_bias`` to an arrangement that adds it in its norm kernel, else added here)."""
 
 from __future__ import annotations
 
@@ -54,12 +54,16 @@ class GatedMLP:
         del wg, wu
         self.gate_up = Linear(fused, rt)
         del fused
-        self.gu_bias = None
+        self.gu_bias = self.gu_bias_tc = None
         if "gate_bias" in t:
             bg, bu = (weights.pop(t[r].name).to(torch.float32) for r in ("gate_bias", "up_bias"))
             # in the order of the fused matrix's rows
             self.gu_bias = (torch.stack([bg.view(-1, 16), bu.view(-1, 16)], dim=1).reshape(-1) if self.block
                             else torch.cat([bg, bu])).contiguous()
+            if self.block and self.gate_up._tc is not None:
+                # for the tensor-core product's epilogue: whole row tiles of a CTA pair
+                pad = -self.gu_bias.numel() % kernels.TC_BIAS_PAD
+                self.gu_bias_tc = torch.cat([self.gu_bias, self.gu_bias.new_zeros(pad)]).contiguous()
         self.down = Linear(weights.pop(t["down"].name), rt,
                            bias=weights.pop(t["down_bias"].name) if "down_bias" in t else None)
         self.out_bias, self.defer_out_bias = self.down.bias, False
@@ -79,10 +83,11 @@ class GatedMLP:
         tc = self.gate_up._tc
         scaled = isinstance(x, RowScaled)
         n_tokens = x.shape[0]
-        if tc is not None and self.gu_bias is None and x.dtype == torch.bfloat16 and n_tokens > FUSE_MIN_TOKENS and (
-                scaled or kernels.gemm_tc_supports(x, tc.weight)) and kernels.gemm_tc_gated_supports(self.activation):
-            # the activation is the epilogue of the gate/up product
-            act = tc.gated(x, self.rt.act_dtype, self.block, self.activation)
+        if tc is not None and (self.gu_bias is None or self.gu_bias_tc is not None) and x.dtype == torch.bfloat16 and (
+                n_tokens > FUSE_MIN_TOKENS) and (scaled or kernels.gemm_tc_supports(x, tc.weight)) and (
+                kernels.gemm_tc_gated_supports(self.activation)):
+            # the activation (and the biases of gate and up) are the epilogue of the gate/up product
+            act = tc.gated(x, self.rt.act_dtype, self.block, self.activation, bias=self.gu_bias_tc)
         else:
             assert not scaled
             gu = self.gate_up(x, splits_ok=True)

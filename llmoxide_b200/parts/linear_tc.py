@@ -110,14 +110,15 @@ class TensorCoreLinear:
             return x.x, (x.sumsq, x.n_parts, x.eps, x.d)
         return x, None
 
-    def gated(self, x, out_dtype, block: int = 0, activation="silu"):
+    def gated(self, x, out_dtype, block: int = 0, activation="silu", bias=None):
         """act(gate x) * (up x), [T, N/2] (SiLU unless ``activation`` says otherwise, ``kernels.gate_act_args``);
         ``block`` = 0 for weight = [gate rows; up rows], 16 for blocks of 16 gate rows each followed by the 16 up
-        rows of the same features."""
+        rows of the same features.  ``bias`` (block 16 only): float32 per row of the weight, in the weight's row
+        order, zero-padded to a multiple of ``kernels.TC_BIAS_PAD``; added before the activation."""
         x, scale = self._unpack(x)
         out = scratch((x.shape[0], self.N // 2), out_dtype, x.device, "output of the gated matrix product")
         kernels.gemm_tc(x, self.weight, out, gated=2 if block == 16 else 1, pair=x.shape[0] > PAIR_MIN_TOKENS,
-                        scale=scale, activation=activation)
+                        scale=scale, activation=activation, gate_bias=bias)
         return out
 
 def plan_for(weight: torch.Tensor, n_sm: int = 148):

@@ -527,7 +527,7 @@ def test_experts_with_a_shared_expert_against_the_plain_mixture(d, F, E, top, sh
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("d, F", [(96, 80), (100, 36), (256, 384)])
+@pytest.mark.parametrize("d, F", [(96, 80), (100, 36), (256, 384), (128, 400)])
 def test_gated_feed_forward_with_tanh_gelu_and_biases(d, F, dtype):
     """down(gelu_tanh(gate x + b_g) * (up x + b_u)) + b_d; the output bias is the part's own to add when no
     arrangement has taken it over."""
