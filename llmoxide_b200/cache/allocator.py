@@ -52,6 +52,7 @@ def host_library():
         for name in ("release", "unreserve", "n_free_pages"):
             getattr(lib, f"llmx_alloc_{name}").argtypes = [c_void_p, c_int]
         lib.llmx_alloc_set_keep_first.argtypes = [c_void_p, c_int, c_int]
+        lib.llmx_alloc_set_every.argtypes = [c_void_p, c_int, c_int, c_int]
         for name in ("reserve", "commit"):
             getattr(lib, f"llmx_alloc_{name}").argtypes = [c_void_p, c_int, c_longlong]
         lib.llmx_alloc_commit_many.argtypes = [c_void_p, c_int, c_void_p, c_void_p]
@@ -88,10 +89,12 @@ def raise_host_error(code: int) -> None:
 
 class CacheAllocator:
     """Slots, pages and lengths.  ``windows[g]`` is group g's window or None; ``keep_first[g]`` how many of a
-    sequence's first positions stay visible under the window (their pages are never given back)."""
+    sequence's first positions stay visible under the window (their pages are never given back).  ``every[g]`` = (n,
+    pages) makes group g hold one row per n positions (row b exists once the sequence holds positions b*n .. b*n+n-1),
+    out of a pool of ``pages`` pages of its own; None or n = 1: a row per position out of ``n_pages``."""
 
     def __init__(self, n_slots: int, n_pages: int, windows: list, max_seq_len: Optional[int] = None,
-                 keep_first: Optional[list] = None):
+                 keep_first: Optional[list] = None, every: Optional[list] = None):
         if n_slots <= 0 or n_pages <= 0:
             raise ValueError("the cache needs at least one slot and one page")
         self.n_slots, self.n_pages = n_slots, n_pages
@@ -106,6 +109,11 @@ class CacheAllocator:
         for g, n in enumerate(self.keep_first):
             if n:
                 self._ok(self._lib.llmx_alloc_set_keep_first(self._h, g, n))
+        self.every = [(1, n_pages) if not e or e[0] <= 1 else (int(e[0]), int(e[1]))
+                      for e in (every or [None] * len(self.windows))]
+        for g, (n, pages) in enumerate(self.every):
+            if n > 1:
+                self._ok(self._lib.llmx_alloc_set_every(self._h, g, n, pages))
         self._row = (c_int * max(1, n_pages))()
 
     def __del__(self):
@@ -176,7 +184,7 @@ class CacheAllocator:
         return list(self._row[:n])
 
     def pages_held(self, group: int = 0) -> int:
-        return self.n_pages - self._lib.llmx_alloc_n_free_pages(self._h, group)
+        return self.every[group][1] - self._lib.llmx_alloc_n_free_pages(self._h, group)
 
     def check_consistent(self) -> None:
         """No page held twice or lost; used by tests."""

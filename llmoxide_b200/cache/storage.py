@@ -28,7 +28,10 @@ class KVNeed:
     ``window`` positions, beside which the first ``keep_first`` positions of a
     sequence stay visible for good.  Values may be narrower or wider than keys
     (``v_head_dim``, default ``head_dim``), and an entry may keep its keys and
-    values in a dtype of its own (default: the runtime's cache dtype)."""
+    values in a dtype of its own (default: the runtime's cache dtype).  With ``pool`` n > 1 the entry owns a second
+    store beside the first, one key and one value per block of n positions (block b = positions b*n .. b*n+n-1, its
+    row exists once the sequence holds all of them); that store keeps every row, whatever the window.  ``every`` is
+    how many positions one row of a store stands for (the second store's description; 1 for the first)."""
 
     n_kv_heads: int
     head_dim: int
@@ -36,6 +39,12 @@ class KVNeed:
     v_head_dim: Optional[int] = None
     dtype: Optional[torch.dtype] = None
     keep_first: int = 0
+    pool: int = 0
+    every: int = 1
+
+    def pooled(self) -> "KVNeed":
+        """The description of the store of one row per block that goes with this entry."""
+        return KVNeed(self.n_kv_heads, self.head_dim, None, self.v_head_dim, self.dtype, 0, 0, self.pool)
 
 
 @dataclass(frozen=True)
@@ -55,6 +64,10 @@ class CacheEntryView:
     v: Optional[torch.Tensor]       # [n_pages, G, PAGE, D of the values]
     state: Optional[torch.Tensor]   # [n_slots, *shape]
     need: Optional[KVNeed]
+    # the store of one row per block of ``need.pool`` positions, where the entry has one
+    pool_group: Optional[int] = None
+    pool_k: Optional[torch.Tensor] = None
+    pool_v: Optional[torch.Tensor] = None
 
 
 class Cache:
@@ -68,20 +81,28 @@ class Cache:
         self.n_pages = n_pages
         self.groups: list = []          # KVNeed per group
         self._entry_group: list = []    # entry -> (group, index in group) or None
+        self._entry_pool: dict = {}     # entry -> (group, index in group) of its store of one row per block
         members: dict = {}
-        for kv, _ in needs:
-            if kv is None:
-                self._entry_group.append(None)
-                continue
+
+        def join(kv, entry):
             if kv not in members:
                 members[kv] = []
                 self.groups.append(kv)
-            g = self.groups.index(kv)
-            self._entry_group.append((g, len(members[kv])))
-            members[kv].append(len(self._entry_group) - 1)
+            members[kv].append(entry)
+            return self.groups.index(kv), len(members[kv]) - 1
+
+        for e, (kv, _) in enumerate(needs):
+            if kv is None:
+                self._entry_group.append(None)
+                continue
+            self._entry_group.append(join(kv, e))
+            if kv.pool > 1:
+                self._entry_pool[e] = join(kv.pooled(), e)
+        # a store of one row per n positions: a sequence of L positions holds L / n rows, in whole pages
+        pages_of = lambda kv: n_pages if kv.every <= 1 else n_pages // kv.every + n_slots + 1
         self.k_store, self.v_store = [], []
         for kv in self.groups:
-            k_shape = (len(members[kv]), n_pages, kv.n_kv_heads, PAGE, kv.head_dim)
+            k_shape = (len(members[kv]), pages_of(kv), kv.n_kv_heads, PAGE, kv.head_dim)
             v_shape = k_shape[:-1] + (kv.v_head_dim or kv.head_dim,)
             # (every long-lived buffer carries guard words behind it: guard.py)
             g = len(self.k_store)
@@ -93,7 +114,8 @@ class Cache:
         ]
         self.alloc = CacheAllocator(n_slots, n_pages, [kv.window for kv in self.groups] or [None],
                                     max_seq_len=max_seq_len,
-                                    keep_first=[kv.keep_first for kv in self.groups] or [0])
+                                    keep_first=[kv.keep_first for kv in self.groups] or [0],
+                                    every=[(kv.every, pages_of(kv)) for kv in self.groups] or None)
         self._has_groups = bool(self.groups)
 
     # ---- slots -------------------------------------------------------------
@@ -118,7 +140,11 @@ class Cache:
         if eg is None:
             return CacheEntryView(None, None, None, self.state_store[entry], None)
         g, i = eg
-        return CacheEntryView(g, self.k_store[g][i], self.v_store[g][i], self.state_store[entry], self.groups[g])
+        view = CacheEntryView(g, self.k_store[g][i], self.v_store[g][i], self.state_store[entry], self.groups[g])
+        if entry in self._entry_pool:
+            pg, pi = self._entry_pool[entry]
+            view.pool_group, view.pool_k, view.pool_v = pg, self.k_store[pg][pi], self.v_store[pg][pi]
+        return view
 
     def n_groups(self) -> int:
         return len(self.groups)

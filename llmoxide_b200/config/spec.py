@@ -58,6 +58,7 @@ class BlockSpec:
     norms: Mapping[str, PartSpec]         # role in the arrangement -> norm
     position: Optional[PartSpec] = None   # position encoding handed to the mixer
     params: Mapping[str, Any] = field(default_factory=dict)   # the arrangement's own constants
+    tensors: Mapping[str, TensorSpec] = field(default_factory=dict)   # the arrangement's own tensors, by role
 
 
 @dataclass(frozen=True)
@@ -127,6 +128,8 @@ class ModelSpec:
             for p in parts:
                 for t in p.tensors.values():
                     add(t)
+            for t in b.tensors.values():
+                add(t)
         for t in self.final_norm.tensors.values():
             add(t)
         for t in self.head.tensors.values():

@@ -15,6 +15,11 @@
 // With `chunk` > 0 positions are cut into chunks of that many, counted from the sequence's position 0, and a
 // query sees only the keys of its own chunk: first = p - p % chunk (beside a window, the later of the two).
 //
+// With `pool` > 0 every block of `pool` positions that lies wholly before the window (block b = positions
+// b*pool .. b*pool+pool-1, seen from p when b*pool+pool-1 <= p - window) is seen as one key and one value: row b of
+// a second store (pool_k, pool_v, with a block table of its own), taken first, in the same softmax.
+// With `gate` a head's output is multiplied by sigmoid(gate[t * gate_stride + hq]).
+//
 // One warp per (token, head).  Keys are taken 32 at a time starting at the
 // range's first key: lane j scores key lo + c*32 + j with a sequential dot over
 // D, the chunk's maximum and sum update a running softmax, and the lanes then
@@ -28,11 +33,14 @@
 
 template <typename TA, typename TC>
 __global__ void attention_paged_kernel(const TA* __restrict__ q, TA* __restrict__ out,
-                                       const TC* __restrict__ k_cache, const TC* __restrict__ v_cache,
+                                       const TC* __restrict__ k_cache_w, const TC* __restrict__ v_cache_w,
                                        const int* __restrict__ block_table, int table_width,
                                        const int* __restrict__ token_seq, const int* __restrict__ token_pos,
                                        int H, int G, int D, int Dv, size_t q_stride, int window, int keep_first,
-                                       float scale, float sink, int chunk) {
+                                       float scale, float sink, int chunk, int pool,
+                                       const TC* __restrict__ pool_k, const TC* __restrict__ pool_v,
+                                       const int* __restrict__ pool_table, const float* __restrict__ gate,
+                                       size_t gate_stride) {
   extern __shared__ float q_buf[];  // [ATT_WARPS][D]
   pdl_launch_dependents();
   pdl_wait();
@@ -44,7 +52,7 @@ __global__ void attention_paged_kernel(const TA* __restrict__ q, TA* __restrict_
   const int p = token_pos[t];
   int first = (window > 0 && p - (window - 1) > 0) ? p - (window - 1) : 0;
   if (chunk > 0) first = max(first, p - p % chunk);
-  const int* pages = block_table + (size_t)token_seq[t] * table_width;
+  const int* pages = block_table + (size_t)token_seq[t] * table_width;     // (re-pointed per range below)
 
   float* qs = q_buf + warp * D;
   const TA* qrow = q + (size_t)t * q_stride + (size_t)hq * D;
@@ -57,10 +65,19 @@ __global__ void attention_paged_kernel(const TA* __restrict__ q, TA* __restrict_
   for (int i = 0; i < MAX_OWN; ++i) acc[i] = 0.f;
   float m = -INFINITY, l = 0.f;
 
-  // two ranges of keys: the kept first ones that lie before the window, then the window up to p
-  const int n_kept = keep_first < first ? keep_first : first;
+  // two ranges of keys: the kept first ones that lie before the window (or the pooled blocks that do, out of their
+  // own store), then the window up to p
+  int n_kept = keep_first < first ? keep_first : first;
+  if (pool > 0) n_kept = p - window + 1 >= pool ? (p - window + 1) / pool : 0;
+  const int* pages_w = pages;
+  const int* pages_0 = pool > 0 ? pool_table + (size_t)token_seq[t] * table_width : pages;
+  const TC* kc0 = pool > 0 ? pool_k : k_cache_w;
+  const TC* vc0 = pool > 0 ? pool_v : v_cache_w;
   for (int range = n_kept > 0 ? 0 : 1; range < 2; ++range) {
   const int lo = range ? first : 0, last = range ? p : n_kept - 1;
+  const TC* k_cache = range ? k_cache_w : kc0;
+  const TC* v_cache = range ? v_cache_w : vc0;
+  pages = range ? pages_w : pages_0;
   for (int base = lo; base <= last; base += 32) {
     const int j = base + lane;
     const bool live = j <= last;
@@ -92,7 +109,8 @@ __global__ void attention_paged_kernel(const TA* __restrict__ q, TA* __restrict_
   }
   }
   // a sink: `sink` keys of score 0 that have no value; they only add to the denominator
-  const float inv = 1.0f / (sink > 0.f ? l + sink * expf(-m) : l);
+  float inv = 1.0f / (sink > 0.f ? l + sink * expf(-m) : l);
+  if (gate) inv *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_stride + hq]));
   TA* orow = out + ((size_t)t * H + hq) * Dv;
 #pragma unroll
   for (int i = 0; i < MAX_OWN; ++i) {
@@ -101,13 +119,20 @@ __global__ void attention_paged_kernel(const TA* __restrict__ q, TA* __restrict_
   }
 }
 
-LLMX_API int llmx_attention_paged_chunked(const void* q, void* out, int act_dtype, const void* k_cache,
+// pool > 0: pool_k / pool_v hold one row per block of `pool` positions, paged like the cache, with the block table
+// pool_table (as wide as block_table); needs a window and no kept first keys.  gate: null, or float32 with
+// gate[t * gate_stride + head] the logit of head's output gate.
+LLMX_API int llmx_attention_paged_pooled(const void* q, void* out, int act_dtype, const void* k_cache,
                                   const void* v_cache, int cache_dtype, const int* block_table, int table_width,
                                   const int* token_seq, const int* token_pos, int n_tokens, int H, int G, int D,
                                   int Dv, long long q_stride, int window, int keep_first, float scale, float sink,
-                                  int chunk, cudaStream_t stream) {
+                                  int chunk, int pool, const void* pool_k, const void* pool_v, const int* pool_table,
+                                  const float* gate, long long gate_stride, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (chunk < 0 || (chunk > 0 && keep_first > 0)) return LLMX_REFUSED(1);
+  if (pool < 0 || (pool > 0 && (window <= 0 || keep_first > 0 || chunk > 0 || !pool_k || !pool_v || !pool_table)))
+    return LLMX_REFUSED(1);
+  if (gate && gate_stride < H) return LLMX_REFUSED(1);
   if (H <= 0 || G <= 0 || H % G != 0 || D <= 0 || D > ATT_MAX_D || window < 0) return LLMX_REFUSED(1);
   if (Dv <= 0 || Dv > ATT_MAX_D || keep_first < 0 || q_stride < (long long)H * D) return LLMX_REFUSED(1);
   dim3 grid(n_tokens, (H + ATT_WARPS - 1) / ATT_WARPS);
@@ -115,7 +140,8 @@ LLMX_API int llmx_attention_paged_chunked(const void* q, void* out, int act_dtyp
 #define CASE(TA, TC)                                                                                      \
   launch_pdl(attention_paged_kernel<TA, TC>, grid, dim3(ATT_WARPS * 32), smem, stream,                    \
       (const TA*)q, (TA*)out, (const TC*)k_cache, (const TC*)v_cache, block_table, table_width, token_seq, \
-      token_pos, H, G, D, Dv, (size_t)q_stride, window, keep_first, scale, sink, chunk)
+      token_pos, H, G, D, Dv, (size_t)q_stride, window, keep_first, scale, sink, chunk, pool, (const TC*)pool_k,  \
+      (const TC*)pool_v, pool_table, gate, (size_t)gate_stride)
   if (act_dtype == LLMX_F32 && cache_dtype == LLMX_F32) CASE(float, float);
   else if (act_dtype == LLMX_BF16 && cache_dtype == LLMX_BF16) CASE(bf16, bf16);
   else if (act_dtype == LLMX_F32 && cache_dtype == LLMX_BF16) CASE(float, bf16);
@@ -123,6 +149,16 @@ LLMX_API int llmx_attention_paged_chunked(const void* q, void* out, int act_dtyp
   else return LLMX_REFUSED(2);
 #undef CASE
   return LLMX_LAUNCH_STATUS();
+}
+
+LLMX_API int llmx_attention_paged_chunked(const void* q, void* out, int act_dtype, const void* k_cache,
+                                  const void* v_cache, int cache_dtype, const int* block_table, int table_width,
+                                  const int* token_seq, const int* token_pos, int n_tokens, int H, int G, int D,
+                                  int Dv, long long q_stride, int window, int keep_first, float scale, float sink,
+                                  int chunk, cudaStream_t stream) {
+  return llmx_attention_paged_pooled(q, out, act_dtype, k_cache, v_cache, cache_dtype, block_table, table_width,
+                                     token_seq, token_pos, n_tokens, H, G, D, Dv, q_stride, window, keep_first, scale,
+                                     sink, chunk, 0, nullptr, nullptr, nullptr, nullptr, 0, stream);
 }
 
 LLMX_API int llmx_attention_paged(const void* q, void* out, int act_dtype, const void* k_cache,
@@ -133,4 +169,68 @@ LLMX_API int llmx_attention_paged(const void* q, void* out, int act_dtype, const
   return llmx_attention_paged_chunked(q, out, act_dtype, k_cache, v_cache, cache_dtype, block_table, table_width,
                                       token_seq, token_pos, n_tokens, H, G, D, Dv, q_stride, window, keep_first, scale,
                                       sink, 0, stream);
+}
+
+// ---------------------------------------------------------------------------
+// The store of one row per block of `pool` positions: when a step writes the last position of block b
+// (position b*pool + pool - 1), that block's key is the mean of its `pool` keys as the cache holds them, its value
+// the mean of the values, summed in float32 from the block's first position to its last, times 1 / pool, and
+// stored as row b of the second store.  One warp per (token, kv head); a token that ends no block does nothing.
+// The cache must still hold the block's positions: its window is at least `pool`.
+// ---------------------------------------------------------------------------
+template <typename TC>
+__global__ void pool_blocks_kernel(const TC* __restrict__ k_cache, const TC* __restrict__ v_cache,
+                                   const int* __restrict__ block_table, TC* __restrict__ pool_k,
+                                   TC* __restrict__ pool_v, const int* __restrict__ pool_table, int table_width,
+                                   const int* __restrict__ token_seq, const int* __restrict__ token_pos, int G, int D,
+                                   int Dv, int pool, int n_pages, int n_pool_pages) {
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x, g = blockIdx.y * ATT_WARPS + warp;
+  if (g >= G) return;
+  const int p = token_pos[t];
+  if ((p + 1) % pool != 0) return;
+  const int b = p / pool;
+  const int* pages = block_table + (size_t)token_seq[t] * table_width;
+  const int dst_page = pool_table[(size_t)token_seq[t] * table_width + b / LLMX_PAGE];
+  if (dst_page < 0 || dst_page >= n_pool_pages) {
+    if (lane == 0) llmx_report(1);
+    return;
+  }
+  pdl_wait();
+  const float inv = 1.0f / (float)pool;
+  for (int i = lane; i < D + Dv; i += 32) {
+    const bool is_k = i < D;
+    const int dim = is_k ? i : i - D, width = is_k ? D : Dv;
+    const TC* src = is_k ? k_cache : v_cache;
+    float sum = 0.f;
+    for (int j = p - pool + 1; j <= p; ++j) {
+      const int page = pages[j / LLMX_PAGE];
+      if (page < 0 || page >= n_pages) {
+        llmx_report(2);
+        return;
+      }
+      sum += to_f32(src[cache_row_offset(page, g, j % LLMX_PAGE, G, width) + dim]);
+    }
+    TC* dst = is_k ? pool_k : pool_v;
+    dst[cache_row_offset(dst_page, g, b % LLMX_PAGE, G, width) + dim] = from_f32<TC>(sum * inv);
+  }
+}
+
+LLMX_API int llmx_pool_blocks(const void* k_cache, const void* v_cache, int cache_dtype, const int* block_table,
+                              void* pool_k, void* pool_v, const int* pool_table, int table_width, const int* token_seq,
+                              const int* token_pos, int n_tokens, int G, int D, int Dv, int pool, long long n_pages,
+                              long long n_pool_pages, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (G <= 0 || D <= 0 || Dv <= 0 || pool < 1 || n_pages < 1 || n_pool_pages < 1) return LLMX_REFUSED(1);
+  dim3 grid(n_tokens, (G + ATT_WARPS - 1) / ATT_WARPS);
+#define CASE(TC)                                                                                              \
+  launch_pdl(pool_blocks_kernel<TC>, grid, dim3(ATT_WARPS * 32), 0, stream, (const TC*)k_cache,                \
+             (const TC*)v_cache, block_table, (TC*)pool_k, (TC*)pool_v, pool_table, table_width, token_seq,    \
+             token_pos, G, D, Dv, pool, (int)n_pages, (int)n_pool_pages)
+  if (cache_dtype == LLMX_F32) CASE(float);
+  else if (cache_dtype == LLMX_BF16) CASE(bf16);
+  else return LLMX_REFUSED(2);
+#undef CASE
+  return LLMX_LAUNCH_STATUS();
 }

@@ -42,6 +42,7 @@ LIBRARIES = {
     "gemm_fma": (["gemm_fma.cu"], []),
     "gemm_tc": (["gemm_tc.cu"], []),
     "linear_attention": (["linear_attention.cu"], []),
+    "latent_attention": (["latent_attention.cu"], []),
     "moe": (["moe.cu"], []),
     "post_norm": (["post_norm.cu"], []),
     "moe_tc": (["moe_tc.cu"], []),

@@ -72,12 +72,15 @@ struct Allocator {
   long long max_seq_len;
   std::vector<int> windows;                  // per group; <= 0: every earlier key
   std::vector<int> keep_first;               // per group with a window: the first positions stay visible for good
+  std::vector<int> every;                    // per group: one cached row per `every` positions (1: a row per position);
+                                             // row b of such a group belongs to positions b*every .. b*every+every-1
+                                             // and exists once the sequence holds all of them
   std::vector<Pool> pools;
   std::vector<Slot> slots;
   std::vector<int> free_slots;               // back() is handed out next
 
   Allocator(int ns, int np, const int* w, int ng, long long max_len)
-      : n_slots(ns), n_pages(np), max_seq_len(max_len), windows(w, w + ng), keep_first(ng, 0), slots(ns) {
+      : n_slots(ns), n_pages(np), max_seq_len(max_len), windows(w, w + ng), keep_first(ng, 0), every(ng, 1), slots(ns) {
     for (int g = 0; g < ng; ++g) pools.emplace_back(np);
     for (int s = ns - 1; s >= 0; --s) free_slots.push_back(s);
   }
@@ -128,15 +131,16 @@ struct Allocator {
       g_info[0] = new_len, g_info[1] = max_seq_len;
       return fail(OVERFLOW_SEQ, "%lld tokens do not fit the longest sequence the cache allows of %lld", new_len, max_seq_len);
     }
-    const long long want = pages_for(new_len);
     for (size_t g = 0; g < pools.size(); ++g) {
-      const long long need = want - (long long)st->pages[g].size();
+      const long long need = pages_for(new_len / every[g]) - (long long)st->pages[g].size();
       if (need > pools[g].n_free())
         return fail(EXHAUSTED, "slot %d needs %lld more cache pages for %lld positions, %d of %d are free", slot, need,
                     new_len, pools[g].n_free(), pools[g].n_pages);
     }
-    for (size_t g = 0; g < pools.size(); ++g)
+    for (size_t g = 0; g < pools.size(); ++g) {
+      const long long want = pages_for(new_len / every[g]);
       while ((long long)st->pages[g].size() < want) st->pages[g].push_back(pools[g].take());
+    }
     st->reserved = std::max(st->reserved, new_len);
     return OK;
   }
@@ -145,8 +149,8 @@ struct Allocator {
   int unreserve(int slot) {
     Slot* st = live(slot);
     if (!st) return MISUSE;
-    const size_t keep = (size_t)pages_for(st->length);
     for (size_t g = 0; g < pools.size(); ++g) {
+      const size_t keep = (size_t)pages_for(st->length / every[g]);
       auto& pages = st->pages[g];
       for (size_t i = keep; i < pages.size(); ++i)
         if (pages[i] >= 0 && pools[g].give_back(pages[i])) return MISUSE;
@@ -316,6 +320,17 @@ LLMX_API int llmx_alloc_set_keep_first(void* a, int group, int n) {
   Allocator* al = static_cast<Allocator*>(a);
   if (group < 0 || group >= (int)al->keep_first.size() || n < 0) return fail(BAD_VALUE, "no group %d, or a negative count", group);
   al->keep_first[group] = n;
+  return OK;
+}
+// Group `group` holds one row per `every` positions and has a pool of `n_pages` pages of its own (set before any
+// sequence is live).
+LLMX_API int llmx_alloc_set_every(void* a, int group, int every, int n_pages) {
+  Allocator* al = static_cast<Allocator*>(a);
+  if (group < 0 || group >= (int)al->every.size() || every < 1 || n_pages < 1)
+    return fail(BAD_VALUE, "no group %d, or a stride or page count below one", group);
+  if (al->free_slots.size() != (size_t)al->n_slots) return fail(MISUSE, "a group's stride is set before any sequence is live");
+  al->every[group] = every;
+  al->pools[group] = Pool(n_pages);
   return OK;
 }
 LLMX_API void llmx_alloc_delete(void* a) { delete static_cast<Allocator*>(a); }

@@ -579,3 +579,41 @@ LLMX_API int llmx_moe_extras(const void* x, int x_dtype, long long ldx, const in
 #undef GO
   return LLMX_LAUNCH_STATUS();
 }
+
+// ---------------------------------------------------------------------------
+// Routing by a table: a token's experts are row `token id` of an integer table [vocab, top], each with the same
+// weight.  An id outside the vocabulary or an expert outside [0, E) is reported (code 3) and expert 0 stands in,
+// so that nothing later indexes with it.
+// ---------------------------------------------------------------------------
+__global__ void moe_table_route_kernel(const int* __restrict__ tokens, const int* __restrict__ table, int vocab,
+                                       int E, int top, float weight, int* __restrict__ ids, float* __restrict__ wts,
+                                       int n_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_tokens * top) return;
+  const int t = i / top, k = i % top;
+  const int tok = tokens[t];
+  int e = 0;
+  if (tok < 0 || tok >= vocab) {
+    llmx_report(3);
+  } else {
+    e = table[(size_t)tok * top + k];
+    if (e < 0 || e >= E) {
+      llmx_report(3);
+      e = 0;
+    }
+  }
+  ids[i] = e;
+  wts[i] = weight;
+}
+
+LLMX_API int llmx_moe_table_route(const int* tokens, const int* table, int vocab, int E, int top, float weight, int* ids,
+                                  float* wts, int n_tokens, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (vocab <= 0 || E <= 0 || top <= 0 || top > E) return LLMX_REFUSED(1);
+  const int n = n_tokens * top;
+  launch_pdl(moe_table_route_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, tokens, table, vocab, E, top, weight,
+             ids, wts, n_tokens);
+  return LLMX_LAUNCH_STATUS();
+}

@@ -5,6 +5,7 @@
 //   y = w0 * sum_s delta0[s][t,:] (+ w1 * sum_s delta1[s][t,:]) (+ bias)
 //                                                     partials added in the order s = 0..S-1; a second group of
 //                                                     partials is what a second mixer beside the first returned
+//   y = y * sigmoid(z[t,:] + zb)                      when a gate z is given (z: partials added in order like a group's)
 //   y = norm(y) * post_gain                           when post_gain is given (else y joins as it is)
 //   v = h[t,:] + y;  h[t,:] = v when write_h
 //   out[r,:] = norm(v) * gain                         when out is given
@@ -73,10 +74,26 @@ __device__ __forceinline__ float pn_group1(const PnGroup& g, size_t at) {
   return y * g.weight;
 }
 
+// The gate on a result: y * sigmoid(z + zb), z a group of partials with weight 1, zb float32 [d] or null.
+__device__ __forceinline__ float pn_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float4 pn_gated4(float4 y, const PnGroup& gz, const float* zb, size_t at, int col) {
+  float4 z = pn_group4(gz, at);
+  if (zb) {
+    const float4 b = pn_load4(zb + col);
+    z.x += b.x, z.y += b.y, z.z += b.z, z.w += b.w;
+  }
+  return make_float4(y.x * pn_sigmoid(z.x), y.y * pn_sigmoid(z.y), y.z * pn_sigmoid(z.z), y.w * pn_sigmoid(z.w));
+}
+__device__ __forceinline__ float pn_gated1(float y, const PnGroup& gz, const float* zb, size_t at, int col) {
+  float z = pn_group1(gz, at);
+  if (zb) z += zb[col];
+  return y * pn_sigmoid(z);
+}
+
 template <typename TO, bool VEC>
 __global__ void __launch_bounds__(512)
-post_norm_add_norm_kernel(float* __restrict__ h, const PnGroup g0, const PnGroup g1,
-                          const float* __restrict__ bias, const float* __restrict__ post_gain, int post_center,
+post_norm_add_norm_kernel(float* __restrict__ h, const PnGroup g0, const PnGroup g1, const PnGroup gz,
+                          const float* __restrict__ zb, const float* __restrict__ bias, const float* __restrict__ post_gain, int post_center,
                           float post_eps, const int* __restrict__ rows, const float* __restrict__ gain, int center,
                           float eps, TO* __restrict__ out, int d, int write_h) {
   extern __shared__ __align__(16) float pn_row[];       // [d]
@@ -99,6 +116,7 @@ post_norm_add_norm_kernel(float* __restrict__ h, const PnGroup g0, const PnGroup
           const float4 b = pn_load4(bias + i);
           y.x += b.x, y.y += b.y, y.z += b.z, y.w += b.w;
         }
+        if (gz.p) y = pn_gated4(y, gz, zb, at0 + i, i);
         pn_store4(pn_row + i, y);
       }
     } else {
@@ -106,6 +124,7 @@ post_norm_add_norm_kernel(float* __restrict__ h, const PnGroup g0, const PnGroup
         float y = pn_group1(g0, at0 + i);
         if (g1.p) y += pn_group1(g1, at0 + i);
         if (bias) y += bias[i];
+        if (gz.p) y = pn_gated1(y, gz, zb, at0 + i, i);
         pn_row[i] = y;
       }
     }
@@ -181,8 +200,8 @@ __device__ __forceinline__ void pn_stats_reg(const float4 (&v)[NV], const bool (
 
 template <typename TO, int NV>
 __global__ void __launch_bounds__(512)
-post_norm_add_norm_reg_kernel(float* __restrict__ h, const PnGroup g0, const PnGroup g1,
-                              const float* __restrict__ bias, const float* __restrict__ post_gain, int post_center,
+post_norm_add_norm_reg_kernel(float* __restrict__ h, const PnGroup g0, const PnGroup g1, const PnGroup gz,
+                              const float* __restrict__ zb, const float* __restrict__ bias, const float* __restrict__ post_gain, int post_center,
                               float post_eps, const int* __restrict__ rows, const float* __restrict__ gain, int center,
                               float eps, TO* __restrict__ out, int d, int write_h) {
   __shared__ float red[32];
@@ -219,6 +238,7 @@ post_norm_add_norm_reg_kernel(float* __restrict__ h, const PnGroup g0, const PnG
           const float4 b = pn_load4(bias + col[k]);
           y.x += b.x, y.y += b.y, y.z += b.z, y.w += b.w;
         }
+        if (gz.p) y = pn_gated4(y, gz, zb, at0 + col[k], col[k]);
       }
       v[k] = y;
     }
@@ -258,12 +278,18 @@ post_norm_add_norm_reg_kernel(float* __restrict__ h, const PnGroup g0, const PnG
 // h float32 [T, d]; delta0 / delta1: null, or n_split partials [T, d] split_stride elements apart, each group
 // times its weight (delta1 only beside delta0); bias, post_gain, gain: float32 [d] or null; rows: int32 [n_rows]
 // or null (every row of h); out: [n_rows, d] or null.
-LLMX_API int llmx_post_norm_add_norm(float* h, const void* delta0, int dtype0, int n_split0, long long stride0,
+// gate: null, or n_split partials [T, d] whose sum (+ gate_bias, float32 [d] or null) is the logit of the gate on y.
+LLMX_API int llmx_post_norm_add_norm_gated(float* h, const void* delta0, int dtype0, int n_split0, long long stride0,
                                      float weight0, const void* delta1, int dtype1, int n_split1, long long stride1,
                                      float weight1, const float* bias, const float* post_gain, int post_center,
                                      float post_eps, const int* rows, int n_rows, const float* gain, int center,
-                                     float eps, void* out, int out_dtype, int d, int write_h, cudaStream_t stream) {
+                                     float eps, void* out, int out_dtype, int d, int write_h, const void* gate,
+                                     int gate_dtype, int gate_split, long long gate_stride, const float* gate_bias,
+                                     cudaStream_t stream) {
   if (n_rows <= 0) return 0;
+  if (gate && (!delta0 || gate_split < 1 || (gate_dtype != LLMX_F32 && gate_dtype != LLMX_BF16))) return LLMX_REFUSED(1);
+  const PnGroup gz = {gate, gate_split, gate_dtype == LLMX_BF16, (size_t)gate_stride, 1.0f};
+  const float* zb = gate ? gate_bias : nullptr;
   if (d <= 0 || (delta0 && n_split0 < 1) || (delta1 && (n_split1 < 1 || !delta0)) || (out && !gain))
     return LLMX_REFUSED(1);
   if ((delta0 && dtype0 != LLMX_F32 && dtype0 != LLMX_BF16) || (delta1 && dtype1 != LLMX_F32 && dtype1 != LLMX_BF16))
@@ -277,7 +303,8 @@ LLMX_API int llmx_post_norm_add_norm(float* h, const void* delta0, int dtype0, i
     return !g.p || (!((uintptr_t)g.p & (4 * esz - 1)) && g.stride % 4 == 0);
   };
   const int osz = out_dtype == LLMX_F32 ? 4 : 2;
-  const bool vec = d % 4 == 0 && !((uintptr_t)h & 15) && aligned(g0) && aligned(g1) && !((uintptr_t)bias & 15) &&
+  const bool vec = d % 4 == 0 && !((uintptr_t)h & 15) && aligned(g0) && aligned(g1) && aligned(gz) &&
+                   !((uintptr_t)zb & 15) && !((uintptr_t)bias & 15) &&
                    !((uintptr_t)post_gain & 15) && !((uintptr_t)gain & 15) && !((uintptr_t)out & (4 * osz - 1));
   int threads = ((d + 3) / 4 + 31) / 32 * 32;
   threads = threads < 64 ? 64 : threads > 512 ? 512 : threads;
@@ -288,7 +315,7 @@ LLMX_API int llmx_post_norm_add_norm(float* h, const void* delta0, int dtype0, i
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                      \
       if (e != cudaSuccess) return (int)e;                                                                               \
     }                                                                                                                    \
-    launch_pdl(post_norm_add_norm_kernel<TO, VEC>, dim3(n_rows), dim3(threads), smem, stream, h, g0, g1, bias,           \
+    launch_pdl(post_norm_add_norm_kernel<TO, VEC>, dim3(n_rows), dim3(threads), smem, stream, h, g0, g1, gz, zb, bias,   \
                post_gain, post_center, post_eps, rows, gain, center, eps, (TO*)out, d, write_h);                         \
   } while (0)
   if (out && out_dtype != LLMX_BF16 && out_dtype != LLMX_F32) return LLMX_REFUSED(2);
@@ -298,7 +325,7 @@ LLMX_API int llmx_post_norm_add_norm(float* h, const void* delta0, int dtype0, i
     const int nv = n4 > 1024 ? 4 : n4 > 128 ? 2 : 1;
     const int reg_threads = ((n4 + nv - 1) / nv + 31) / 32 * 32;
 #define GO_REG(TO, NV)                                                                                                   \
-    launch_pdl(post_norm_add_norm_reg_kernel<TO, NV>, dim3(n_rows), dim3(reg_threads), 0, stream, h, g0, g1, bias,       \
+    launch_pdl(post_norm_add_norm_reg_kernel<TO, NV>, dim3(n_rows), dim3(reg_threads), 0, stream, h, g0, g1, gz, zb, bias, \
                post_gain, post_center, post_eps, rows, gain, center, eps, (TO*)out, d, write_h)
     if (out_bf16) {
       if (nv == 4) GO_REG(bf16, 4); else if (nv == 2) GO_REG(bf16, 2); else GO_REG(bf16, 1);
@@ -315,6 +342,16 @@ LLMX_API int llmx_post_norm_add_norm(float* h, const void* delta0, int dtype0, i
   }
 #undef GO
   return LLMX_LAUNCH_STATUS();
+}
+
+LLMX_API int llmx_post_norm_add_norm(float* h, const void* delta0, int dtype0, int n_split0, long long stride0,
+                                     float weight0, const void* delta1, int dtype1, int n_split1, long long stride1,
+                                     float weight1, const float* bias, const float* post_gain, int post_center,
+                                     float post_eps, const int* rows, int n_rows, const float* gain, int center,
+                                     float eps, void* out, int out_dtype, int d, int write_h, cudaStream_t stream) {
+  return llmx_post_norm_add_norm_gated(h, delta0, dtype0, n_split0, stride0, weight0, delta1, dtype1, n_split1, stride1,
+                                       weight1, bias, post_gain, post_center, post_eps, rows, n_rows, gain, center, eps,
+                                       out, out_dtype, d, write_h, nullptr, LLMX_F32, 1, 0, nullptr, stream);
 }
 
 // y[t, :] += bias for a product's output that no later kernel of this file reads (y: [n_rows, d], float32 or

@@ -341,3 +341,75 @@ LLMX_API int llmx_conv_state_update(const void* proj, int in_dtype, int n_split,
     return LLMX_REFUSED(2);
   return LLMX_LAUNCH_STATUS();
 }
+
+// ---------------------------------------------------------------------------
+// A sublayer's input with its own short convolution added: out_p = x_p + sum_j w[j] * x_(p - taps + 1 + j), per
+// channel, zeros before the sequence's start (tap-major weights [taps][C] as above; the last tap meets x_p itself).
+// Rows before the step's first token come from the sequence's state (the last taps-1 rows of x, float32
+// [slot][taps-1][C], oldest first).  One thread per (token, channel); taps oldest first, then x_p.  With
+// `inline_state` (every sequence brings one token) the thread, the only reader of its channel's state, moves the
+// state on itself; otherwise llmx_conv_state_update does so afterwards.
+// ---------------------------------------------------------------------------
+template <typename TX>
+__global__ void residual_conv_kernel(const TX* __restrict__ x, float* state, int inline_state,
+                                     const float* __restrict__ conv_w, int taps, TX* __restrict__ out,
+                                     const int* __restrict__ token_seq, const int* __restrict__ token_pos,
+                                     const int* __restrict__ seq_start, const int* __restrict__ seq_past,
+                                     const int* __restrict__ seq_slot, size_t C, int n_tokens, int n_seqs,
+                                     int n_slots) {
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int b = token_seq[t], pos = token_pos[t];
+  if (b < 0 || b >= n_seqs || pos < 0) {
+    if (threadIdx.x == 0) llmx_report(1);
+    return;
+  }
+  const int p0 = seq_past[b], row0 = seq_start[b], slot = seq_slot[b];
+  if (p0 < 0 || p0 > pos || row0 < 0 || row0 + (pos - p0) >= n_tokens || slot < 0 || slot >= n_slots) {
+    if (threadIdx.x == 0) llmx_report(1);
+    return;
+  }
+  const int keep = taps - 1;
+  float* st = keep > 0 ? state + (size_t)slot * keep * C : nullptr;
+  const bool move = inline_state && st && pos == p0 && seq_start[b + 1] - row0 == 1;
+  pdl_wait();
+  for (size_t c = (size_t)blockIdx.y * blockDim.x + threadIdx.x; c < C; c += (size_t)gridDim.y * blockDim.x) {
+    float y = 0.f;
+    for (int j = 0; j < taps; ++j) {
+      const int q = pos - keep + j;                       // the position this tap reads
+      float u;
+      if (q >= p0) u = to_f32(x[(size_t)(row0 + q - p0) * C + c]);
+      else u = st[(size_t)(keep - (p0 - q)) * C + c];     // row i of the state is position p0 - keep + i
+      y += conv_w[(size_t)j * C + c] * u;
+    }
+    const float own = to_f32(x[(size_t)t * C + c]);
+    out[(size_t)t * C + c] = from_f32<TX>(own + y);
+    if (move) {
+      for (int i = 0; i + 1 < keep; ++i) st[(size_t)i * C + c] = st[(size_t)(i + 1) * C + c];
+      st[(size_t)(keep - 1) * C + c] = own;
+    }
+  }
+}
+
+// x, out [T, C] (float32 or bfloat16, the same); conv_w float32 [taps, C]; state float32 [slots, taps-1, C].
+LLMX_API int llmx_residual_conv(const void* x, int dtype, float* state, int inline_state, const float* conv_w,
+                                int taps, void* out, const int* token_seq, const int* token_pos,
+                                const int* seq_start, const int* seq_past, const int* seq_slot, int n_tokens,
+                                long long C, int n_seqs, int n_slots, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (C <= 0 || taps < 1 || taps > SC_MAX_TAPS || !conv_w || (taps > 1 && !state)) return LLMX_REFUSED(1);
+  const int threads = C >= 256 ? 256 : 128;
+  const long long per_row = (C + threads - 1) / threads;
+  dim3 grid(n_tokens, (unsigned)(per_row < 64 ? per_row : 64));
+  if (dtype == LLMX_F32)
+    launch_pdl(residual_conv_kernel<float>, grid, dim3(threads), 0, stream, (const float*)x, state, inline_state, conv_w,
+               taps, (float*)out, token_seq, token_pos, seq_start, seq_past, seq_slot, (size_t)C, n_tokens, n_seqs,
+               n_slots);
+  else if (dtype == LLMX_BF16)
+    launch_pdl(residual_conv_kernel<bf16>, grid, dim3(threads), 0, stream, (const bf16*)x, state, inline_state, conv_w,
+               taps, (bf16*)out, token_seq, token_pos, seq_start, seq_past, seq_slot, (size_t)C, n_tokens, n_seqs,
+               n_slots);
+  else
+    return LLMX_REFUSED(2);
+  return LLMX_LAUNCH_STATUS();
+}

@@ -122,7 +122,7 @@ def _library(lib_name: str):
 # waited for a step anyway (no copy, no extra synchronisation).
 
 _STATUS_SLOTS = {"gemm_tc": 0, "attention_prefill_tc": 1, "attention_decode": 2, "sampling": 3, "moe_tc": 4,
-                 "short_conv": 5, "stream_mix": 6, "moe": 7}
+                 "short_conv": 5, "stream_mix": 6, "moe": 7, "attention": 8, "latent_attention": 9}
 _STATUS_MEANING = {
     "gemm_tc": {1: "the producer's wait for a free stage ran out", 2: "the MMA issuer's wait for a stage's data ran out",
                 3: "the epilogue's wait for an accumulator ran out", 4: "the MMA issuer's wait for a drained accumulator ran out",
@@ -138,7 +138,11 @@ _STATUS_MEANING = {
                    2: "a sequence's rows or slot lie outside the launch's arrays (state update)"},
     "stream_mix": {1: "a wanted row lies outside the stream"},
     "moe": {1: "a token's router scores hold a NaN (no expert compares greater than none)",
-            2: "an expert id outside the router's experts reached the sort"},
+            2: "an expert id outside the router's experts reached the sort",
+            3: "a token id outside the routing table, or a table entry that names no expert"},
+    "attention": {1: "a block's row has no page in the store of one row per block",
+                  2: "a block's positions are no longer held by the cache"},
+    "latent_attention": {1: "a token's sequence, position or page lies outside the launch's arrays"},
 }
 _status_host = None
 
@@ -147,7 +151,7 @@ def status_words() -> torch.Tensor:
     """The page-locked int32 words, one per library that reports (see ``_STATUS_SLOTS``)."""
     global _status_host
     if _status_host is None:
-        _status_host = torch.zeros(8, dtype=torch.int32).pin_memory()
+        _status_host = torch.zeros(16, dtype=torch.int32).pin_memory()
     return _status_host
 
 
@@ -326,6 +330,28 @@ def conv_state_update(proj, state, taps: int, ctx) -> None:
              ctx.n_seqs, C, proj.shape[-2], state.shape[0], _stream()), "conv_state_update")
 
 
+CONV_MAX_TAPS = 16     # the same constant as SC_MAX_TAPS in short_conv.cu
+
+
+def residual_conv(x, state, conv_w, taps: int, out, ctx, inline_state: bool = False) -> None:
+    """out = x + conv(x): a causal convolution over time on every channel, y_p = sum_j w[j] x_(p - taps + 1 + j),
+    zeros before a sequence's start.  x, out [T, C] of one dtype; ``conv_w`` float32 [taps, C]; ``state`` float32
+    [slots, taps-1, C], the last taps-1 rows of x of every sequence (read here; moved on here as well when
+    ``inline_state`` and every sequence brings one token, else by ``conv_state_update``)."""
+    _dev(x, state, conv_w, out)
+    _contig("x", x), _contig("out", out), _contig("conv_w", conv_w)
+    C = x.shape[1]
+    assert out.shape == x.shape and out.dtype == x.dtype and conv_w.dtype == torch.float32 and conv_w.shape == (taps, C)
+    assert taps == 1 or (state is not None and state.dtype == torch.float32 and state.shape[1:] == (taps - 1, C)
+                         and state.is_contiguous())
+    f = _fn("short_conv", "llmx_residual_conv",
+            [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_int, c_longlong, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _tag(x), _ptr(state), int(inline_state), _ptr(conv_w), taps, _ptr(out), _ptr(ctx.token_seq),
+             _ptr(ctx.token_pos), _ptr(ctx.seq_start), _ptr(ctx.seq_past), _ptr(ctx.seq_slot), x.shape[0], C, ctx.n_seqs,
+             state.shape[0] if state is not None else 0, _stream()), "residual_conv")
+
+
 def softcap(x: torch.Tensor, cap: float) -> None:
     """x = cap * tanh(x / cap) in place; x float32, contiguous."""
     _dev(x)
@@ -382,12 +408,14 @@ def add_rms_norm(h: torch.Tensor, delta, gain: torch.Tensor, eps: float, out, ro
 
 
 def post_norm_add_norm(h, groups, bias, post_gain, post_center: bool, post_eps: float, gain, center: bool, eps: float,
-                       out, rows=None, write_h: bool = True) -> None:
+                       out, rows=None, write_h: bool = True, gate=None) -> None:
     """A sublayer's result normed before it joins the residual stream ``h`` (float32 [T, d], in place), and the norm
     the next sublayer reads.  ``groups``: up to two (delta, weight), delta [T, d] or split partials [S, T, d] summed
     in order; y = sum_g weight_g * delta_g + ``bias``; with ``post_gain`` y = norm(y) * post_gain; v = h + y (stored
     when ``write_h``); with ``out`` out[r] = norm(v[rows[r]]) * gain (every row without ``rows``).  A norm with
-    ``center`` subtracts the mean (layer norm without bias), without it is an RMS norm; both are float32."""
+    ``center`` subtracts the mean (layer norm without bias), without it is an RMS norm; both are float32.
+    ``gate`` = (z, b): y is multiplied by sigmoid(z + b) element by element before its norm; z [T, d] or split
+    partials [S, T, d], b float32 [d] or None."""
     deltas = [g[0] for g in groups]
     _dev(h, bias, post_gain, gain, out, rows, *deltas)
     assert h.dtype == torch.float32 and h.dim() == 2 and len(groups) <= 2
@@ -407,11 +435,23 @@ def post_norm_add_norm(h, groups, bias, post_gain, post_center: bool, post_eps: 
     if out is not None:
         _contig("out", out)
         assert out.shape[0] >= n_rows and out.shape[-1] == d
-    f = _fn("post_norm", "llmx_post_norm_add_norm",
+    gate_args = [None, F32, 1, 0, None]
+    if gate is not None:
+        z, zb = gate
+        _dev(z, zb)
+        _contig("gate", z)
+        assert groups, "a gate multiplies a result"
+        if z.dim() == 2:
+            z = z.unsqueeze(0)
+        assert z.shape[1:] == h.shape and (zb is None or (zb.dtype == torch.float32 and zb.numel() == d
+                                                          and zb.is_contiguous()))
+        gate_args = [_ptr(z), _tag(z), z.shape[0], z.stride(0), _ptr(zb)]
+    f = _fn("post_norm", "llmx_post_norm_add_norm_gated",
             [c_void_p, c_void_p, c_int, c_int, c_longlong, c_float, c_void_p, c_int, c_int, c_longlong, c_float, c_void_p,
-             c_void_p, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_int, c_void_p])
+             c_void_p, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_int,
+             c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p])
     _check(f(_ptr(h), *args, _ptr(bias), _ptr(post_gain), int(post_center), post_eps, _ptr(rows), n_rows, _ptr(gain),
-             int(center), eps, _ptr(out), _tag(out) if out is not None else F32, d, int(write_h), _stream()),
+             int(center), eps, _ptr(out), _tag(out) if out is not None else F32, d, int(write_h), *gate_args, _stream()),
            "post_norm_add_norm")
 
 
@@ -519,26 +559,94 @@ def sum_splits(parts: torch.Tensor, out: torch.Tensor) -> None:
 
 def attention_paged(q, out, k_cache, v_cache, block_table, token_seq, token_pos, n_heads: int,
                     n_kv_heads: int, head_dim: int, window, scale: float, v_head_dim=None, keep_first: int = 0,
-                    sink: float = 0.0, chunk: int = 0) -> None:
+                    sink: float = 0.0, chunk: int = 0, pool: int = 0, pool_k=None, pool_v=None, pool_table=None,
+                    gate=None) -> None:
     """General attention over the paged cache; q [T,H*D] (rows may be the first columns of wider rows), out
     [T,H*Dv].  Under a window the first ``keep_first`` keys of a sequence stay visible.  ``sink`` is added to the
     softmax's denominator (as many keys of score 0 that have no value).  With ``chunk`` n > 0 a query sees only the
-    keys of its own chunk of n positions, counted from the sequence's position 0."""
-    _dev(q, out, k_cache, v_cache, block_table, token_seq, token_pos)
+    keys of its own chunk of n positions, counted from the sequence's position 0.  With ``pool`` n > 0 (beside a
+    window) every block of n positions that lies wholly before the window is seen as row b of ``pool_k`` / ``pool_v``
+    (paged like the cache, block table ``pool_table``).  ``gate`` float32 [T, >= H] (a view with any row stride):
+    head h's output is multiplied by sigmoid(gate[t, h])."""
+    _dev(q, out, k_cache, v_cache, block_table, token_seq, token_pos, pool_k, pool_v, pool_table, gate)
     _contig("out", out), _contig("block_table", block_table)
+    if pool:
+        _contig("pool_table", pool_table)
+        assert pool_table.shape == block_table.shape and pool_k.dtype == k_cache.dtype == pool_v.dtype
+        assert pool_k.is_contiguous() and pool_v.is_contiguous()
+    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[1] >= n_heads)
     v_head_dim = v_head_dim or head_dim
     assert q.stride(1) == 1 and q.shape[1] >= n_heads * head_dim and out.shape[1] == n_heads * v_head_dim
     if head_dim > 256 or v_head_dim > 256:
         raise Unsupported(f"head_dim {head_dim}/{v_head_dim}: the general attention kernel takes sizes up to 256")
     if n_heads % n_kv_heads:
         raise Unsupported(f"{n_heads} heads are not a multiple of {n_kv_heads} kv heads")
-    f = _fn("attention", "llmx_attention_paged_chunked",
+    f = _fn("attention", "llmx_attention_paged_pooled",
             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
-             c_int, c_int, c_int, c_int, c_int, c_longlong, c_int, c_int, c_float, c_float, c_int, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_longlong, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p,
+             c_void_p, c_void_p, c_void_p, c_longlong, c_void_p])
     _check(f(_ptr(q), _ptr(out), _tag(q), _ptr(k_cache), _ptr(v_cache), _tag(k_cache), _ptr(block_table),
              block_table.shape[1], _ptr(token_seq), _ptr(token_pos), q.shape[0], n_heads, n_kv_heads, head_dim,
              v_head_dim, q.stride(0), int(window or 0), int(keep_first or 0), scale, float(sink or 0.0), int(chunk or 0),
-             _stream()), "attention_paged")
+             int(pool or 0), _ptr(pool_k), _ptr(pool_v), _ptr(pool_table), _ptr(gate),
+             gate.stride(0) if gate is not None else 0, _stream()), "attention_paged")
+
+
+def pool_blocks(k_cache, v_cache, block_table, pool_k, pool_v, pool_table, token_seq, token_pos, n_kv_heads: int,
+                head_dim: int, v_head_dim: int, pool: int) -> None:
+    """For every token of the step that is the last position of a block of ``pool`` positions: the means of the
+    block's keys and values, as the cache holds them, become row ``position // pool`` of ``pool_k`` / ``pool_v``."""
+    _dev(k_cache, v_cache, block_table, pool_k, pool_v, pool_table, token_seq, token_pos)
+    _contig("block_table", block_table), _contig("pool_table", pool_table)
+    assert pool_table.shape == block_table.shape and k_cache.dtype == v_cache.dtype == pool_k.dtype == pool_v.dtype
+    assert all(t.is_contiguous() for t in (k_cache, v_cache, pool_k, pool_v))
+    f = _fn("attention", "llmx_pool_blocks",
+            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+             c_int, c_int, c_int, c_longlong, c_longlong, c_void_p])
+    _check(f(_ptr(k_cache), _ptr(v_cache), _tag(k_cache), _ptr(block_table), _ptr(pool_k), _ptr(pool_v),
+             _ptr(pool_table), block_table.shape[1], _ptr(token_seq), _ptr(token_pos), token_pos.numel(), n_kv_heads,
+             head_dim, v_head_dim, pool, k_cache.shape[0], pool_k.shape[0], _stream()), "pool_blocks")
+
+
+def latent_norms(down, q_gain, kv_gain, eps: float, cq, c, q_rank: int, kv_rank: int) -> None:
+    """The two latents of a latent attention out of its fused first product: ``down`` [T, >= q_rank + kv_rank]
+    (or float32 split partials [S, T, ..]) -> cq = rms(down[:, :q_rank]) * q_gain, c = rms(down[:, q_rank :
+    q_rank + kv_rank]) * kv_gain, float32 statistics, in the dtype of ``cq`` and ``c``."""
+    _dev(down, q_gain, kv_gain, cq, c)
+    _contig("down", down), _contig("cq", cq), _contig("c", c)
+    n_split, stride = (down.shape[0], down.stride(0)) if down.dim() == 3 else (1, 0)
+    T = down.shape[-2]
+    assert cq.shape == (T, q_rank) and c.shape == (T, kv_rank) and cq.dtype == c.dtype
+    assert q_gain.dtype == kv_gain.dtype == torch.float32 and q_gain.numel() == q_rank and kv_gain.numel() == kv_rank
+    f = _fn("latent_attention", "llmx_latent_norms",
+            [c_void_p, c_int, c_int, c_longlong, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int,
+             c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(down), _tag(down), n_split, stride, down.shape[-1], _ptr(q_gain), _ptr(kv_gain), eps, _ptr(cq),
+             _ptr(c), _tag(cq), T, q_rank, kv_rank, _stream()), "latent_norms")
+
+
+def latent_rope_cache(q, kv, down, k_rot_off: int, q_out, k_cache, v_cache, block_table, ctx, cos, sin, n_heads: int,
+                      head_dim: int, rot_dim: int, v_head_dim: int) -> None:
+    """Rotation and cache write of a latent attention.  q [T, H*(R+D)] (every head: rotated part, then unrotated),
+    kv [T, H*D + H*Dv] (unrotated keys, then values), ``down`` as for ``latent_norms`` with the shared rotated key
+    part at columns k_rot_off .. k_rot_off+R-1 -> q_out [T, H*(R+D)], one key [rot(shared) | unrotated] per head
+    and the values into the paged cache entry [pages, H, PAGE, R+D] / [pages, H, PAGE, Dv]."""
+    _dev(q, kv, down, q_out, k_cache, v_cache, block_table, cos, sin)
+    for name, t in (("q", q), ("kv", kv), ("down", down), ("q_out", q_out), ("block_table", block_table)):
+        _contig(name, t)
+    n_split, stride = (down.shape[0], down.stride(0)) if down.dim() == 3 else (1, 0)
+    T, H, D, R, Dv = q.shape[0], n_heads, head_dim, rot_dim, v_head_dim
+    assert q.shape[1] == H * (R + D) == q_out.shape[1] and kv.shape == (T, H * (D + Dv)) and q.dtype == kv.dtype
+    assert k_cache.shape[1:] == (H, PAGE, R + D) and v_cache.shape[1:] == (H, PAGE, Dv) and k_cache.dtype == v_cache.dtype
+    assert cos.shape[1] == R // 2 and cos.dtype == torch.float32 and k_cache.is_contiguous() and v_cache.is_contiguous()
+    f = _fn("latent_attention", "llmx_latent_rope_cache",
+            [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p, c_int, c_void_p,
+             c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+             c_int, c_longlong, c_void_p])
+    _check(f(_ptr(q), _ptr(kv), _tag(q), _ptr(down), _tag(down), n_split, stride, down.shape[-1], k_rot_off,
+             _ptr(q_out), _tag(q_out), _ptr(k_cache), _ptr(v_cache), _tag(k_cache), _ptr(block_table),
+             block_table.shape[1], _ptr(ctx.token_seq), _ptr(ctx.token_pos), _ptr(cos), _ptr(sin), T, H, D, R, Dv,
+             ctx.n_seqs, k_cache.shape[0], _stream()), "latent_rope_cache")
 
 
 def n_sm(device=None) -> int:
@@ -971,6 +1079,19 @@ def moe_route(logits, ids, weights, top: int, n_groups: int, keep_groups: int, g
              c_void_p, c_void_p])
     _check(f(_ptr(logits), _ptr(ids), _ptr(weights), T, E, top, n_groups, keep_groups, group_top, _SCORES[score],
              int(normalize), norm_eps, scale, _ptr(bias), _stream()), "moe_route")
+
+
+def moe_table_route(tokens, table, n_experts: int, weight: float, ids, weights) -> None:
+    """Routing by a table: token t's experts are row ``tokens[t]`` of the int32 ``table`` [vocab, top], each with
+    ``weight``; -> ids int32 [T, top], weights float32 [T, top]."""
+    _dev(tokens, table, ids, weights)
+    _contig("table", table), _contig("ids", ids), _contig("weights", weights), _contig("tokens", tokens)
+    assert table.dtype == torch.int32 and tokens.dtype == torch.int32 and ids.dtype == torch.int32
+    assert weights.dtype == torch.float32 and ids.shape == weights.shape == (tokens.numel(), table.shape[1])
+    f = _fn("moe", "llmx_moe_table_route",
+            [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p])
+    _check(f(_ptr(tokens), _ptr(table), table.shape[0], n_experts, table.shape[1], weight, _ptr(ids), _ptr(weights),
+             tokens.numel(), _stream()), "moe_table_route")
 
 
 def moe_max_tiles(n_pairs: int, n_experts: int, tile_rows: int = MOE_TILE) -> int:

@@ -2,7 +2,7 @@
 position encodings and their arrangement in a block.  Each takes its sizes
 and constants as parameters; none knows which model it is in."""
 
-from . import (attention, block, embedding, experts, feed_forward, head, linear_attention, mlstm, norm,  # noqa: F401
+from . import (attention, block, embedding, experts, feed_forward, head, latent_attention, linear_attention, mlstm, norm,  # noqa: F401
                position, side_by_side)  # noqa: F401  (register the built-in kinds)
 from .block import build_block
 from .linear import Linear

@@ -31,6 +31,13 @@ learned scalar l (tensor ``v_mix``) before they are cached.
 ``chunk`` n > 0: positions are cut into chunks of n, counted from position 0 of
 the sequence, and a query sees the keys j <= p of its own chunk only
 (floor(j / n) = floor(p / n)); the cache entry keeps what a window of n would.
+``pool`` n > 1, beside a window: every block of n positions that lies wholly before the window (block b =
+positions b*n .. b*n+n-1, seen from p once b*n+n-1 <= p - window) is seen as one key and one value, the means of the
+block's keys and values as the cache holds them (after norm and rotation), in the same softmax as the window's keys.
+The cache entry then owns a second store of one row per block (``KVNeed.pool``), written when a step brings a
+block's last position; positions that have left the window and whose block is not complete are not seen.  A position
+encoding that pairs neighbouring dimensions is met by reordering the rows of the q and k projections once
+(``parts.position.halves_order``).
 Tensors ``q_bias``, ``k_bias``, ``v_bias``, ``o_bias``: biases of the four
 projections (q, k, v: added where the projected row is read, before norm and
 rotation; o: offered as ``out_bias`` to an arrangement that adds it in its
@@ -45,6 +52,7 @@ from .. import kernels
 from ..cache import KVNeed, StateNeed
 from ..errors import Unsupported
 from .linear import Linear
+from .position import halves_order
 from .registry import register_mixer
 
 
@@ -64,6 +72,15 @@ class GQAttention:
         self.cache_window = spec.get("cache_window", self.window) if "cache_window" in spec.params else self.window
         if self.chunk:
             self.cache_window = self.chunk           # nothing before the last `chunk` positions is seen again
+        self.pool = int(spec.get("pool") or 0)
+        if self.pool == 1:
+            self.pool = 0                            # blocks of one position: every earlier key, as it is
+            self.window = self.cache_window = None
+        if self.pool:
+            if not self.window or self.keep_first or self.chunk or not bool(spec.get("own_kv", True)):
+                raise Unsupported("pooled blocks are built for a layer with its own keys and values under a plain window")
+            # a block's mean is taken from the cache when its last position arrives
+            self.cache_window = max(int(self.cache_window or 0), self.pool)
         self.cache_keep_first = int(spec.get("cache_keep_first", self.keep_first) or 0) if self.cache_window else 0
         self.own_kv = bool(spec.get("own_kv", True))
         self.eps = float(spec.get("qk_norm_eps") or 0.0)
@@ -78,6 +95,7 @@ class GQAttention:
             wq, wk, wv = (weights.pop(t[r].name) for r in ("q", "k", "v"))
             if not (wq.dtype == wk.dtype == wv.dtype):
                 wq, wk, wv = wq.float(), wk.float(), wv.float()
+            wq, wk = halves_order(position, wq, self.H, self.D), halves_order(position, wk, self.G, self.D)
             # One matrix product for q, k and v: rows of q, then k, then v.
             wqkv = torch.cat([wq, wk, wv], dim=0)
             del wq, wk, wv
@@ -85,15 +103,17 @@ class GQAttention:
             self.q_only = Linear(wqkv[: self.H * self.D], rt)
         else:
             self.qkv = None
-            self.q_only = Linear(weights.pop(t["q"].name), rt)
+            self.q_only = Linear(halves_order(position, weights.pop(t["q"].name), self.H, self.D), rt)
         self.o = Linear(weights.pop(t["o"].name), rt, bias=weights.pop(t["o_bias"].name) if "o_bias" in t else None)
         self.out_bias, self.defer_out_bias = self.o.bias, False
         self.qkv_bias = None
         if "q_bias" in t:
             if not self.own_kv:
                 raise Unsupported("projection biases are built for a layer with its own keys and values")
-            self.qkv_bias = torch.cat([weights.pop(t[r].name).to(torch.float32) for r in ("q_bias", "k_bias", "v_bias")]
-                                      ).contiguous()
+            bq, bk, bv = (weights.pop(t[r].name).to(torch.float32) for r in ("q_bias", "k_bias", "v_bias"))
+            bq = halves_order(position, bq.unsqueeze(1), self.H, self.D).squeeze(1)
+            bk = halves_order(position, bk.unsqueeze(1), self.G, self.D).squeeze(1)
+            self.qkv_bias = torch.cat([bq, bk, bv]).contiguous()
         self.q_gain = self.k_gain = None
         if "q_norm" in t:
             self.q_gain = weights.pop(t["q_norm"].name).to(torch.float32).contiguous()
@@ -122,7 +142,7 @@ class GQAttention:
     def cache_need(self):
         state = StateNeed((self.taps - 1, self.channels)) if self.taps > 1 else None
         return KVNeed(self.G, self.D, self.cache_window, v_head_dim=None if self.Dv == self.D else self.Dv,
-                      keep_first=self.cache_keep_first), state
+                      keep_first=self.cache_keep_first, pool=self.pool), state
 
     @property
     def takes_row_scales(self) -> bool:
@@ -133,7 +153,7 @@ class GQAttention:
         libs = {"elementwise"} | self.q_only.libraries() | self.o.libraries()
         if self.staged:
             libs.add("short_conv")
-        if not self.plain:
+        if not self.plain or self.pool:
             return libs | {"attention"}
         if self.rt.dtype == "bfloat16" and self.rt.tensor_cores:
             libs |= {"attention_decode",
@@ -186,6 +206,9 @@ class GQAttention:
             kernels.qk_norm_rope_cache(qkv, q, view.k, view.v, block_table, ctx.token_seq, ctx.token_pos,
                                        self.q_gain, self.k_gain, self.eps, cos, sin, n_rot, H, G, D, writes_cache,
                                        v_head_dim=Dv, bias=self.qkv_bias)
+        if self.pool and writes_cache:
+            kernels.pool_blocks(view.k, view.v, block_table, view.pool_k, view.pool_v, ctx.block_tables[view.pool_group],
+                                ctx.token_seq, ctx.token_pos, G, D, Dv, self.pool)
         out = torch.empty((T, H * Dv), dtype=self.rt.act_dtype, device=dev)
         self.attend(q, out, view, block_table, ctx)
         if self.out_bias is None and residual is not None and self.o.add_into(out, residual):
@@ -199,7 +222,7 @@ class GQAttention:
         size than the keys among them) and always in float32.  All of them take
         a window that keeps its first keys, and a chunked mask."""
         H, G, D = self.H, self.G, self.D
-        fast = (self.plain and q.dtype == torch.bfloat16 and view.k.dtype == torch.bfloat16
+        fast = (self.plain and q.dtype == torch.bfloat16 and view.k.dtype == torch.bfloat16 and not self.pool
                 and self.rt.tensor_cores and self.scale > 0)       # (the tiled kernels take the maximum before the scale)
         if fast and ctx.is_decode:
             kernels.attention_decode(q, out, view.k, view.v, block_table, ctx.seq_past, H, G, D, self.window,
@@ -215,4 +238,6 @@ class GQAttention:
         else:
             kernels.attention_paged(q, out, view.k, view.v, block_table, ctx.token_seq, ctx.token_pos,
                                     H, G, D, self.window, self.scale, v_head_dim=self.Dv, keep_first=self.keep_first,
-                                    sink=self.sink, chunk=self.chunk)
+                                    sink=self.sink, chunk=self.chunk, pool=self.pool, pool_k=view.pool_k,
+                                    pool_v=view.pool_v,
+                                    pool_table=ctx.block_tables[view.pool_group] if self.pool else None)

@@ -11,6 +11,12 @@ stream (``residual=h``) and may add its result there itself, in the kernel of it
 last product; it then returns None, and the norm that follows has nothing to add.
 ``sandwich`` norms a sublayer's result as well as its input: h += norm_b(mixer(norm_a(h))), then the same around
 the feed-forward; the norm behind a sublayer, the residual add and the norm before the next sublayer are one kernel.
+Two options of ``sandwich`` (``BlockSpec.params`` and ``BlockSpec.tensors``): ``mixer_conv_taps`` n > 0, the mixer
+reads u + conv(u) instead of the normed stream u, conv a causal convolution over time on every channel (tensor
+``mixer_conv`` [width, n]; the last n - 1 rows of u of a sequence are its state, kept in the cache entry's state area);
+``result_gate`` "sigmoid", every sublayer's result is multiplied by sigmoid(W u + b) before the norm behind it (tensors
+``mixer_gate`` / ``mixer_gate_bias``, ``feed_forward_gate`` / ``feed_forward_gate_bias``; u is the normed stream, before
+the convolution); the product W u is one more matrix product, sigmoid and multiplication happen in the norm kernel.
 A part whose last product has a bias offers it as ``out_bias``; an arrangement that can add it in its own norm
 kernel sets the part's ``defer_out_bias``, and the part then leaves the bias to it."""
 
@@ -19,6 +25,9 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
+from ..cache import StateNeed
+from ..errors import Unsupported
+from .linear import Linear
 from .registry import (ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, lookup, register_arrangement)
 
 
@@ -231,16 +240,49 @@ class SandwichBlock:
         for part in (self.mixer, self.feed_forward):
             if getattr(part, "out_bias", None) is not None:
                 part.defer_out_bias = True           # added by the norm kernel behind the part
+        self.width = spec.norms["mixer"]["size"]
+        self.taps = int(spec.params.get("mixer_conv_taps") or 0)
+        self.conv_w = None
+        if self.taps:
+            if self.taps > kernels.CONV_MAX_TAPS:
+                raise Unsupported(f"{self.taps} taps: the convolution kernels take up to {kernels.CONV_MAX_TAPS}")
+            # [channels, taps] -> tap-major [taps, channels]: neighbouring threads read neighbouring channels of a tap
+            self.conv_w = weights.pop(spec.tensors["mixer_conv"].name).to(torch.float32).t().contiguous()
+        gate = spec.params.get("result_gate")
+        if gate not in (None, "sigmoid"):
+            raise Unsupported(f"result_gate {gate!r}: 'sigmoid' or none")
+        self.mixer_gate = self.ff_gate = None
+        if gate:
+            t = spec.tensors
+            self.mixer_gate = Linear(weights.pop(t["mixer_gate"].name), rt, bias=weights.pop(t["mixer_gate_bias"].name))
+            if self.ff_norm is not None:
+                self.ff_gate = Linear(weights.pop(t["feed_forward_gate"].name), rt,
+                                      bias=weights.pop(t["feed_forward_gate_bias"].name))
 
     def cache_need(self):
-        return self.mixer.cache_need()
+        kv, state = self.mixer.cache_need()
+        if self.taps > 1:
+            if state is not None:
+                raise Unsupported("a convolution before a mixer that keeps state of its own is not built")
+            state = StateNeed((self.taps - 1, self.width))
+        return kv, state
 
     def libraries(self) -> set:
-        libs = set()
-        for part in (self.mixer_norm, self.mixer_post, self.ff_norm, self.ff_post, self.mixer, self.feed_forward):
+        libs = {"short_conv"} if self.taps else set()
+        for part in (self.mixer_norm, self.mixer_post, self.ff_norm, self.ff_post, self.mixer, self.feed_forward,
+                     self.mixer_gate, self.ff_gate):
             if part is not None:
                 libs |= getattr(part, "libraries", set)()
         return libs
+
+    def _convolved(self, x, ctx, view):
+        """u + conv(u), and the state moved on by the step's rows."""
+        out = torch.empty_like(x)
+        inline = bool(ctx.is_decode and self.taps > 1)
+        kernels.residual_conv(x, view.state, self.conv_w, self.taps, out, ctx, inline_state=inline)
+        if self.taps > 1 and not inline:
+            kernels.conv_state_update(x, view.state, self.taps, ctx)
+        return out
 
     def forward(self, h, pending, ctx, view, writes_cache=True):
         probe = getattr(ctx, "probe", None)
@@ -249,16 +291,25 @@ class SandwichBlock:
             pending = None
             probe("resid_in", h)
         x = self.mixer_norm.add_forward(h, pending)
-        a = self.mixer.forward(x, ctx, view, writes_cache)
+        # the gate's logits come from the normed stream itself; its bias, the sigmoid and the multiplication are
+        # the norm kernel's
+        gate = None
+        if self.mixer_gate is not None:
+            gate = (self.mixer_gate(x, out_dtype=torch.float32, splits_ok=True, add_bias=False), self.mixer_gate.bias)
+        u = self._convolved(x, ctx, view) if self.taps else x
+        a = self.mixer.forward(u, ctx, view, writes_cache)
         if probe:
             probe("attn_norm", x), probe("attn_output", _summed(a))
-        pending = self.mixer_post.owed(a, bias=getattr(self.mixer, "out_bias", None))
+        pending = self.mixer_post.owed(a, bias=getattr(self.mixer, "out_bias", None), gate=gate)
         if self.ff_norm is None:
             return pending
         x = self.ff_norm.add_forward(h, pending)
+        gate = None
+        if self.ff_gate is not None:
+            gate = (self.ff_gate(x, out_dtype=torch.float32, splits_ok=True, add_bias=False), self.ff_gate.bias)
         out = self.feed_forward.forward(x, ctx)
         if probe:
             probe("attn_residual", h), probe("attn_post_norm", x)
             if out is not None:
                 probe("ffn_out", _summed(out))
-        return self.ff_post.owed(out, bias=getattr(self.feed_forward, "out_bias", None))
+        return self.ff_post.owed(out, bias=getattr(self.feed_forward, "out_bias", None), gate=gate)

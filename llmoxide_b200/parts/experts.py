@@ -5,7 +5,8 @@ Router logits z = W_r x are float32 (the router's matrix is kept in float32;
 x may be the compute dtype's rounding), plus the tensor ``router_bias`` when
 there is one.  ``score``: s = sigmoid(z), or a softmax over z, or
 "softmax_top": the ``top`` largest z win and their weights are the softmax
-over those z alone.  With ``n_groups`` > 1 the expert indices are cut into
+over those z alone; or "table": there is no router, the integer tensor ``table`` [vocab, top] names every token
+id's experts, and each counts ``table_weight``.  With ``n_groups`` > 1 the expert indices are cut into
 ``n_groups`` contiguous blocks of equal length; every block is ranked by the
 sum of its ``group_score_top`` highest s, and a token's choice is restricted
 to the ``keep_groups`` top-ranked blocks.  The ``top`` highest s among the
@@ -75,8 +76,16 @@ class RoutedExperts:
         if self.E_all > 1024 or self.top > 16:
             raise Unsupported(f"{self.E_all} experts / top {self.top}: the routing kernel takes up to 1024 / 16")
         t = spec.tensors
+        self.table = None
+        if self.score == "table":
+            if self.n_identity or self.n_groups != 1 or "router" in t or spec.get("shared_size"):
+                raise Unsupported("routing by a table is built for plain experts without groups or a shared expert")
+            self.table = weights.pop(t["table"].name).to(torch.int32).contiguous()
+            self.table_weight = float(spec.get("table_weight", 1.0 / self.top))
+            if self.table.dim() != 2 or self.table.shape[1] != self.top:
+                raise ConfigError(f"the routing table has shape {tuple(self.table.shape)}, expected [vocab, {self.top}]")
         # the router decides in float32 whatever the compute dtype
-        self.router = weights.pop(t["router"].name).to(torch.float32).contiguous()
+        self.router = None if self.table is not None else weights.pop(t["router"].name).to(torch.float32).contiguous()
         self.correction = (weights.pop(t["correction"].name).to(torch.float32).contiguous()
                            if "correction" in t else None)
         self.router_bias = (weights.pop(t["router_bias"].name).to(torch.float32).contiguous()
@@ -123,9 +132,12 @@ class RoutedExperts:
         ids = torch.empty((T, self.top), dtype=torch.int32, device=dev)
         pair_w = torch.empty((T, self.top), dtype=torch.float32, device=dev)
         shared_z = torch.empty((T, 1), dtype=torch.float32, device=dev) if self.shared and self.shared_gated else None
-        kernels.moe_router(x, self.router, ids, pair_w, self.n_groups, self.keep_groups, self.group_top, self.score,
-                           self.normalize, self.norm_eps, self.scale, bias=self.correction, extra_out=shared_z,
-                           logit_bias=self.router_bias)
+        if self.table is not None:
+            kernels.moe_table_route(ctx.tokens, self.table, self.E, self.table_weight, ids, pair_w)
+        else:
+            kernels.moe_router(x, self.router, ids, pair_w, self.n_groups, self.keep_groups, self.group_top, self.score,
+                               self.normalize, self.norm_eps, self.scale, bias=self.correction, extra_out=shared_z,
+                               logit_bias=self.router_bias)
         probe = getattr(ctx, "probe", None)
         if probe:
             probe("router_ids", ids), probe("router_weights", pair_w)

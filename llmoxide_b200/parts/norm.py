@@ -47,34 +47,36 @@ class WeightedSum:
 
 class PostNormed:
     """What a sublayer owes the residual stream when its result is normed first:
-    h += norm(sum_g weight_g * delta_g + bias) * gain."""
+    h += norm((sum_g weight_g * delta_g + bias) * sigmoid(z + zb)) * gain, the gate (z, zb) optional."""
 
-    __slots__ = ("terms", "bias", "gain", "center", "eps")
+    __slots__ = ("terms", "bias", "gain", "center", "eps", "gate")
 
-    def __init__(self, terms, bias, gain, center, eps):
-        self.terms, self.bias, self.gain, self.center, self.eps = terms, bias, gain, center, eps
+    def __init__(self, terms, bias, gain, center, eps, gate=None):
+        self.terms, self.bias, self.gain, self.center, self.eps, self.gate = terms, bias, gain, center, eps, gate
 
 
 def _terms(delta):
     return delta.terms if isinstance(delta, WeightedSum) else [(delta, 1.0)]
 
 
-def _owed_normed(norm, delta, bias, center: bool):
+def _owed_normed(norm, delta, bias, center: bool, gate=None):
     if delta is None:
         return None
-    return PostNormed(_terms(delta), bias, norm.gain, center, norm.eps)
+    return PostNormed(_terms(delta), bias, norm.gain, center, norm.eps, gate)
 
 
 def _general_add_norm(h, delta, gain, center: bool, eps: float, out, rows, write_h: bool):
     """h += delta in any of its forms (a tensor, partials, a weighted sum, a normed result); out = norm(h) * gain."""
+    gate = None
     if delta is None:
         terms, bias, post_gain, post_center, post_eps = [], None, None, False, 0.0
     elif isinstance(delta, PostNormed):
         terms, bias, post_gain, post_center, post_eps = delta.terms, delta.bias, delta.gain, delta.center, delta.eps
+        gate = delta.gate
     else:
         terms, bias, post_gain, post_center, post_eps = _terms(delta), None, None, False, 0.0
     kernels.post_norm_add_norm(h, terms, bias, post_gain, post_center, post_eps, gain, center, eps, out, rows=rows,
-                               write_h=write_h)
+                               write_h=write_h, gate=gate)
 
 
 @register_norm("layer_norm")
@@ -90,9 +92,10 @@ class LayerNorm:
     def libraries(self) -> set:
         return {"post_norm"}
 
-    def owed(self, delta, bias=None):
-        """The sublayer's result ``delta`` (None: nothing), to be normed by this norm before it joins the stream."""
-        return _owed_normed(self, delta, bias, self.center)
+    def owed(self, delta, bias=None, gate=None):
+        """The sublayer's result ``delta`` (None: nothing), to be normed by this norm before it joins the stream;
+        ``gate`` = (z, zb): times sigmoid(z + zb) first."""
+        return _owed_normed(self, delta, bias, self.center, gate)
 
     def add(self, h, delta) -> None:
         if delta is not None:
@@ -120,15 +123,16 @@ class RMSNorm:
         self._plain: dict = {}
 
     def libraries(self) -> set:
-        return {"elementwise", "stream_mix"}
+        return {"elementwise", "stream_mix", "post_norm"}
 
-    def owed(self, delta, n_streams: int = 0, bias=None):
+    def owed(self, delta, n_streams: int = 0, bias=None, gate=None):
         """The update by which a sublayer's result ``delta`` (None: nothing) joins ``n_streams`` copies; without
-        ``n_streams``: the result normed by this norm before it joins the one stream (a norm behind a sublayer)."""
+        ``n_streams``: the result normed by this norm before it joins the one stream (a norm behind a sublayer),
+        with ``gate`` = (z, zb) times sigmoid(z + zb) first."""
         if delta is None:
             return None
         if not n_streams:
-            return _owed_normed(self, delta, bias, False)
+            return _owed_normed(self, delta, bias, False, gate)
         if self.mix is None:        # no connection weights: every copy keeps itself and gets mult * delta
             if n_streams not in self._plain:
                 self._plain[n_streams] = (torch.eye(n_streams, dtype=torch.float32, device=self.gain.device).contiguous(),

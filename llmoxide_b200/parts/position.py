@@ -11,7 +11,16 @@ amplitude_slope) the frequencies are stretched for contexts beyond the
 with lo = max(floor(t(fast)), 0), hi = min(ceil(t(slow)), n_rot - 1) and
 t(turns) = n_rot ln(original / (2 pi turns)) / (2 ln base); its frequency becomes
 f_i / factor * ramp_i + f_i (1 - ramp_i), and cos and sin are multiplied by
-amplitude_slope * ln(factor) + 1.  ``none`` rotates nothing."""
+amplitude_slope * ln(factor) + 1.  That is the rule "ramp"; with ``scaling["rule"] = "wavelength"`` (factor, low, high,
+original) a pair keeps its frequency f while its wavelength 2 pi / f is shorter than original / high, turns at
+f / factor when it is longer than original / low, and in between at (1 - s) f / factor + s f with
+s = (original / wavelength - low) / (high - low); cos and sin are not scaled.
+
+``pairing="neighbours"`` says that the design rotates the pairs (2i, 2i+1).  A scalar product of a rotated query and
+a rotated key does not depend on the order of a head's dimensions as long as both have the same, so a mixer brings
+the rows of its query and key projections into the order (0, 2, 4, .., 1, 3, 5, ..) once, when the model is built
+(``halves_order``), and every kernel rotates the pairs (i, i + n_rot/2) as for any other model.  ``none`` rotates
+nothing."""
 
 from __future__ import annotations
 
@@ -30,6 +39,9 @@ class RotaryNeox:
         self.factors = spec.get("factors")  # optional per-pair divisors of the angle
         self.angles = spec.get("angles", "float64")
         self.scaling = spec.get("scaling")
+        self.pairing = spec.get("pairing", "halves")
+        if self.pairing not in ("halves", "neighbours"):
+            raise ValueError(f"pairing {self.pairing!r}: 'halves' or 'neighbours'")
         if self.n_rot % 2:
             raise ValueError(f"n_rot {self.n_rot} must be even")
         self._tables = None
@@ -69,6 +81,21 @@ class RotaryNeox:
         if self.angles != "float32" or self.factors is not None:
             raise ValueError("scaled frequencies are built for angles='float32' without per-pair factors")
         factor, original = float(sc["factor"]), float(sc["original"])
+        if sc.get("rule", "ramp") == "wavelength":
+            low, high = float(sc["low"]), float(sc["high"])
+            freqs = []
+            for f in plain:
+                wave = 2.0 * math.pi / f
+                if wave < original / high:
+                    freqs.append(f)
+                elif wave > original / low:
+                    freqs.append(f / factor)
+                else:
+                    s = (original / wave - low) / (high - low)
+                    freqs.append((1.0 - s) * f / factor + s * f)
+            return freqs, 1.0
+        if sc.get("rule", "ramp") != "ramp":
+            raise ValueError(f"scaling rule {sc['rule']!r}: 'ramp' or 'wavelength'")
         turn = lambda turns: self.n_rot * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
         lo = max(math.floor(turn(float(sc["fast"]))), 0)
         hi = min(math.ceil(turn(float(sc["slow"]))), self.n_rot - 1)
@@ -77,6 +104,19 @@ class RotaryNeox:
             ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
             freqs.append(plain[i] / factor * ramp + plain[i] * (1.0 - ramp))
         return freqs, float(sc.get("amplitude_slope", 0.1)) * math.log(factor) + 1.0
+
+
+def halves_order(position, weight, n_heads: int, head_dim: int, first: int = 0):
+    """The rows of a projection [n_heads * head_dim, in] in the order the rotation kernels pair them: unchanged
+    unless ``position`` pairs neighbours; then, in every head, the rotated dims first .. first + n_rot - 1 become
+    (even ones, then odd ones).  Queries and keys must both go through this."""
+    if position is None or getattr(position, "pairing", "halves") != "neighbours":
+        return weight
+    n_rot = position.n_rot
+    order = list(range(head_dim))
+    order[first : first + n_rot] = [first + i for i in range(0, n_rot, 2)] + [first + i for i in range(1, n_rot, 2)]
+    index = torch.tensor([h * head_dim + i for h in range(n_heads) for i in order], device=weight.device)
+    return weight.index_select(0, index).contiguous()
 
 
 @register_position("none")

@@ -104,8 +104,27 @@ def _storage_dtype(spec: ModelSpec, role: str, dtype=None) -> torch.dtype:
     return {"bfloat16": torch.bfloat16, "float32": torch.float32}[name]
 
 
+def host_table(t, seed: int) -> torch.Tensor:
+    """An integer table of the description.  Its ``init`` is ("distinct_below", n): every row holds different
+    numbers below n, row r the numbers (s_r + c) mod n for its columns c with s_r drawn from the tensor's stream."""
+    if not (isinstance(t.init, tuple) and len(t.init) == 2 and t.init[0] == "distinct_below"):
+        raise ValueError(f"{t.name}: integer tables have no random-weights rule")
+    n = int(t.init[1])
+    rows = int(np.prod(t.shape[:-1], dtype=np.int64))
+    cols = int(t.shape[-1])
+    if cols > n:
+        raise ValueError(f"{t.name}: {cols} different numbers below {n} do not exist")
+    with np.errstate(over="ignore"):
+        z = _mix(np.uint64(_stream_seed(seed, t.name)) + np.arange(1, rows + 1, dtype=np.uint64) * _GOLDEN)
+    start = (z >> np.uint64(33)).astype(np.int64) % n
+    table = (start[:, None] + np.arange(cols, dtype=np.int64)[None, :]) % n
+    return torch.from_numpy(table.astype(np.int32)).view(t.shape)
+
+
 def host_tensor(t, seed: int, dtype: torch.dtype) -> torch.Tensor:
     """One tensor of the description on the host, in ``dtype``."""
+    if t.role == "table":
+        return host_table(t, seed)
     stream = _stream_seed(seed, t.name)
     mean, std = _moments(t)
     n = int(np.prod(t.shape, dtype=np.int64))
@@ -158,8 +177,9 @@ def random_tensors_on_device(spec: ModelSpec, seed: int, dtype: str = "bfloat16"
     out = {}
     for t in spec.tensors():
         stored = _storage_dtype(spec, t.role, storage)
-        if not stored.is_floating_point:
-            raise ValueError(f"{t.name}: integer tables have no random-weights rule")
+        if not stored.is_floating_point:        # integer tables are small: made on the host
+            out[t.name] = host_table(t, seed).to(device)
+            continue
         x = torch.empty(t.shape, dtype=target_dtype(stored, dtype), device=device)
         mean, std = _moments(t)
         kernels.fill_normal(x, _stream_seed(seed, t.name), q, mean, std, stored)
