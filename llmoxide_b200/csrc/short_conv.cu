@@ -365,11 +365,11 @@ __global__ void residual_conv_kernel(const TX* __restrict__ x, float* state, int
     return;
   }
   const int p0 = seq_past[b], row0 = seq_start[b], slot = seq_slot[b];
-  if (p0 < 0 || p0 > pos || row0 < 0 || row0 + (pos - p0) >= n_tokens || slot < 0 || slot >= n_slots) {
+  const int keep = taps - 1;
+  if (p0 < 0 || p0 > pos || row0 < 0 || row0 + (pos - p0) >= n_tokens || (keep > 0 && (slot < 0 || slot >= n_slots))) {
     if (threadIdx.x == 0) llmx_report(1);
     return;
   }
-  const int keep = taps - 1;
   float* st = keep > 0 ? state + (size_t)slot * keep * C : nullptr;
   const bool move = inline_state && st && pos == p0 && seq_start[b + 1] - row0 == 1;
   pdl_wait();
