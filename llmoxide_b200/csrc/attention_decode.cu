@@ -121,7 +121,9 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ seq_past,
                         float* __restrict__ ws, unsigned int* __restrict__ counters, bf16* __restrict__ out, int H,
                         int G, int window, int keep_first, int mask_chunk, float scale_log2, float sink,
-                        int n_chunks, int cluster_merge) {
+                        int n_chunks, int cluster_merge, int pool, const __grid_constant__ CUtensorMap map_pk,
+                        const __grid_constant__ CUtensorMap map_pv, const bf16* __restrict__ pool_k,
+                        const bf16* __restrict__ pool_v, const int* __restrict__ pool_table) {
   using S = DecSmem<D>;
   constexpr int KSTEPS = D / 16;
   constexpr uint32_t TILE_BYTES = 2u * DEC_TILE * D * 2u;        // what one stage's copies bring
@@ -163,7 +165,12 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   // the sequence's first keys, the tiles that hold those and lie wholly before the window's first tile come
   // first in the walk: place v of the walk is tile v, or past them tile t_first + (v - n_kept).
   const int t_first = first / DEC_TILE, t_last = p / DEC_TILE;
-  const int n_kept = keep_first > 0 ? min(t_first, (keep_first + DEC_TILE - 1) / DEC_TILE) : 0;
+  // With pooled blocks (pool > 0) the walk begins with the tiles of the second store instead: its row r stands
+  // for positions r*pool .. r*pool+pool-1 and is seen when r < n_rows = (p - window + 1) / pool.
+  const int n_rows = pool > 0 ? max(0, (p - window + 1) / pool) : 0;
+  const int* pool_pages = pool > 0 ? pool_table + (size_t)b * table_width : nullptr;
+  const int n_kept = pool > 0 ? (n_rows + DEC_TILE - 1) / DEC_TILE
+                              : keep_first > 0 ? min(t_first, (keep_first + DEC_TILE - 1) / DEC_TILE) : 0;
   const int n_walk = n_kept + t_last - t_first + 1;
   const int per_warp = (n_walk - 1 + n_chunks * DEC_WARPS) / (n_chunks * DEC_WARPS);         // ceil(tiles / warps)
   const int tile_lo = (chunk * DEC_WARPS + warp) * per_warp;                                // places of the walk
@@ -175,7 +182,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   auto load_tile = [&](int place, int stage) {
     if (withhold && place == tile_lo && warp == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) return;
     const int key0 = tile_at(place) * DEC_TILE;
-    const int phys = pages[key0 / LLMX_PAGE];
+    const bool pooled = pool > 0 && place < n_kept;
+    const int phys = pooled ? pool_pages[key0 / LLMX_PAGE] : pages[key0 / LLMX_PAGE];
     const uint32_t sK = sKV + stage * 2 * S::TILE, sV = sK + S::TILE, bar = bars + 8 * stage;
     if (S::TMA) {
       if (lane == 0) {
@@ -183,17 +191,19 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         mbar_expect_tx(bar, TILE_BYTES);
 #pragma unroll
         for (int pn = 0; pn < D / 64; ++pn) {
-          tma_load_2d(sK + pn * DEC_PANEL, &map_k, 64 * pn, row, bar);
-          tma_load_2d(sV + pn * DEC_PANEL, &map_v, 64 * pn, row, bar);
+          tma_load_2d(sK + pn * DEC_PANEL, pooled ? &map_pk : &map_k, 64 * pn, row, bar);
+          tma_load_2d(sV + pn * DEC_PANEL, pooled ? &map_pv : &map_v, 64 * pn, row, bar);
         }
       }
     } else {
       constexpr int CHUNKS = D / 8;
       const size_t off = cache_row_offset(phys, g, key0 % LLMX_PAGE, G, D);
+      const bf16* ksrc = pooled ? pool_k : k_cache;
+      const bf16* vsrc = pooled ? pool_v : v_cache;
       for (int idx = lane; idx < DEC_TILE * CHUNKS; idx += 32) {
         const int r = idx / CHUNKS, c = idx % CHUNKS;
-        cp_async16(sK + S::at(r, c), k_cache + off + (size_t)r * D + c * 8);
-        cp_async16(sV + S::at(r, c), v_cache + off + (size_t)r * D + c * 8);
+        cp_async16(sK + S::at(r, c), ksrc + off + (size_t)r * D + c * 8);
+        cp_async16(sV + S::at(r, c), vsrc + off + (size_t)r * D + c * 8);
       }
       cp_async_arrive(bar);
     }
@@ -204,7 +214,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   for (int j = 0; j < D / 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;     // heads 2tq and 2tq + 1
 
-  // Tiles before the new token's own are complete since earlier steps: they start now.
+  // Tiles before the new token's own are complete since earlier steps: they start now.  (So are the rows of the
+  // second store that the token sees: a block is seen only once it lies wholly before the window.)
   int issued = 0;
   for (; issued < DEC_STAGES - 1 && issued < n_tiles && tile_at(tile_lo + issued) < t_last; ++issued)
     load_tile(tile_lo + issued, issued);
@@ -235,10 +246,12 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       if (!ok) break;
       const uint32_t sK = sKV + stage * 2 * S::TILE, sV = sK + S::TILE;
       const int key0 = tile_at(tile_lo + t) * DEC_TILE;
-      if (key0 + DEC_TILE - 1 > p) {
+      const bool pooled = pool > 0 && tile_lo + t < n_kept;
+      const int last_row = pooled ? n_rows - 1 : p;               // the last row of the tile's store that is seen
+      if (key0 + DEC_TILE - 1 > last_row) {
         // rows past the newest key were never written by this sequence: weight 0, but 0 * NaN is NaN
         uint8_t* vt = wsm + stage * 2 * S::TILE + S::TILE;
-        const int valid = p - key0 + 1;
+        const int valid = last_row - key0 + 1;
         for (int idx = lane; idx < (DEC_TILE - valid) * (D / 8); idx += 32) {
           const int r = valid + idx / (D / 8), c = idx % (D / 8);
           *reinterpret_cast<uint4*>(vt + S::at(r, c)) = make_uint4(0u, 0u, 0u, 0u);
@@ -267,7 +280,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 #pragma unroll
         for (int e = 0; e < 2; ++e) {                              // rows gq and gq + 8
           const int key = key0 + 16 * i + gq + 8 * e;
-          const bool vis = (key >= first || key < keep_first) && key <= p;
+          const bool vis = pooled ? key < n_rows : ((key >= first || key < keep_first) && key <= p);
           s[i][2 * e] = vis ? s[i][2 * e] * scale_log2 : -INFINITY;
           s[i][2 * e + 1] = vis ? s[i][2 * e + 1] * scale_log2 : -INFINITY;
           mx0 = fmaxf(mx0, s[i][2 * e]);
@@ -516,7 +529,8 @@ template <int D>
 static int launch_decode(const void* q, void* out, const void* k_cache, const void* v_cache, long long n_pages,
                          const int* block_table, int table_width, const int* seq_past, float* ws, unsigned int* counters, int B, int H, int G,
                          int window, int keep_first, int mask_chunk, float scale, float sink, int n_chunks,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, int pool = 0, const void* pool_k = nullptr, const void* pool_v = nullptr,
+                         long long n_pool_pages = 0, const int* pool_table = nullptr) {
   const int R = H / G;
   const int head_groups = (R + DEC_ROWS - 1) / DEC_ROWS;
   dim3 grid(n_chunks, G * head_groups, B);
@@ -539,17 +553,24 @@ static int launch_decode(const void* q, void* out, const void* k_cache, const vo
     if (make_map(&mk, k_cache, cache_rows, D, D, DEC_TILE, false)) return LLMX_REFUSED(4);
     if (make_map(&mv, v_cache, cache_rows, D, D, DEC_TILE, false)) return LLMX_REFUSED(4);
   }
+  CUtensorMap mpk = mk, mpv = mv;        // the second store's maps (the first's again when there is none)
+  if (DecSmem<D>::TMA && pool > 0) {
+    const uint64_t pool_rows = (uint64_t)n_pool_pages * G * LLMX_PAGE;
+    if (make_map(&mpk, pool_k, pool_rows, D, D, DEC_TILE, false)) return LLMX_REFUSED(4);
+    if (make_map(&mpv, pool_v, pool_rows, D, D, DEC_TILE, false)) return LLMX_REFUSED(4);
+  }
   // up to 8 chunks (the portable cluster size): merged inside a cluster, nothing goes through the workspace
   const int cluster_merge = (n_chunks > 1 && n_chunks <= 8) ? 1 : 0;
   if (cluster_merge)
     launch_pdl_cluster(kernel, grid, dim3(DEC_WARPS * 32), smem, stream, (unsigned)n_chunks, mk, mv, (const bf16*)q,
                        (const bf16*)k_cache, (const bf16*)v_cache, block_table, table_width, seq_past, ws, counters,
                        (bf16*)out, H, G, window, keep_first, mask_chunk, scale * 1.4426950408889634f, sink, n_chunks,
-                       cluster_merge);
+                       cluster_merge, pool, mpk, mpv, (const bf16*)pool_k, (const bf16*)pool_v, pool_table);
   else
     launch_pdl(kernel, grid, dim3(DEC_WARPS * 32), smem, stream, mk, mv, (const bf16*)q, (const bf16*)k_cache,
                (const bf16*)v_cache, block_table, table_width, seq_past, ws, counters, (bf16*)out, H, G, window,
-               keep_first, mask_chunk, scale * 1.4426950408889634f, sink, n_chunks, cluster_merge);
+               keep_first, mask_chunk, scale * 1.4426950408889634f, sink, n_chunks, cluster_merge, pool, mpk, mpv,
+               (const bf16*)pool_k, (const bf16*)pool_v, pool_table);
   return LLMX_LAUNCH_STATUS();
 }
 
@@ -562,12 +583,19 @@ static int launch_decode(const void* q, void* out, const void* k_cache, const vo
 // sink: added to the softmax's denominator (as many keys of score 0 that have no value); 0 for none.
 // mask_chunk n > 0: positions are cut into chunks of n, counted from the sequence's position 0, and the token sees
 // only the keys of its own chunk (beside a window: the later of the two starts; no kept first keys then).
-LLMX_API int llmx_attention_decode_masked(const void* q, void* out, const void* k_cache, const void* v_cache,
+// pool n > 0 (beside a window, without kept first keys or a chunked mask): every block of n positions that lies
+// wholly before the token's window is seen as row b of pool_k / pool_v, a second store [n_pool_pages, G, 64, D]
+// paged like the cache with the block table pool_table (as wide as block_table).
+LLMX_API int llmx_attention_decode_pooled(const void* q, void* out, const void* k_cache, const void* v_cache,
                                           long long n_pages, const int* block_table, int table_width,
                                           const int* seq_past, float* ws, unsigned int* counters, int B, int H, int G,
                                           int D, int window, int keep_first, int mask_chunk, float scale, float sink,
-                                          int n_chunks, cudaStream_t stream) {
+                                          int n_chunks, int pool, const void* pool_k, const void* pool_v,
+                                          long long n_pool_pages, const int* pool_table, cudaStream_t stream) {
   if (B <= 0) return 0;
+  if (pool < 0 || (pool > 0 && (window <= 0 || keep_first > 0 || mask_chunk > 0 || !pool_k || !pool_v || !pool_table ||
+                                n_pool_pages <= 0 || ((uintptr_t)pool_k & 15) || ((uintptr_t)pool_v & 15))))
+    return LLMX_REFUSED(1);
   if (!(sink >= 0.f)) return LLMX_REFUSED(1);
   if (window <= 0) keep_first = 0;
   if (mask_chunk < 0 || (mask_chunk > 0 && keep_first > 0)) return LLMX_REFUSED(1);
@@ -579,13 +607,24 @@ LLMX_API int llmx_attention_decode_masked(const void* q, void* out, const void* 
 #define CASE(DD)                                                                                               \
   case DD:                                                                                                     \
     return launch_decode<DD>(q, out, k_cache, v_cache, n_pages, block_table, table_width, seq_past, ws, counters, \
-                             B, H, G, window, keep_first, mask_chunk, scale, sink, n_chunks, stream)
+                             B, H, G, window, keep_first, mask_chunk, scale, sink, n_chunks, stream, pool, pool_k,   \
+                             pool_v, n_pool_pages, pool_table)
   switch (D) {
     CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
     CASE(144); CASE(160); CASE(176); CASE(192); CASE(208); CASE(224); CASE(240); CASE(256);
     default: return LLMX_REFUSED(1);
   }
 #undef CASE
+}
+
+LLMX_API int llmx_attention_decode_masked(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                          long long n_pages, const int* block_table, int table_width,
+                                          const int* seq_past, float* ws, unsigned int* counters, int B, int H, int G,
+                                          int D, int window, int keep_first, int mask_chunk, float scale, float sink,
+                                          int n_chunks, cudaStream_t stream) {
+  return llmx_attention_decode_pooled(q, out, k_cache, v_cache, n_pages, block_table, table_width, seq_past, ws,
+                                      counters, B, H, G, D, window, keep_first, mask_chunk, scale, sink, n_chunks, 0,
+                                      nullptr, nullptr, 0, nullptr, stream);
 }
 
 LLMX_API int llmx_attention_decode_sink(const void* q, void* out, const void* k_cache, const void* v_cache,

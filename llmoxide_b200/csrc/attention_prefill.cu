@@ -61,7 +61,9 @@ __global__ void __launch_bounds__(PF_THREADS)
 attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ k_cache,
                          const bf16* __restrict__ v_cache, const int* __restrict__ block_table, int table_width,
                          const int* __restrict__ seq_start, const int* __restrict__ seq_past, int H, int G,
-                         int window, int keep_first, int mask_chunk, float scale_log2, float sink) {
+                         int window, int keep_first, int mask_chunk, float scale_log2, float sink, int pool,
+                         const bf16* __restrict__ pool_k, const bf16* __restrict__ pool_v,
+                         const int* __restrict__ pool_table) {
   constexpr int CHUNKS = D / 8;              // 16-byte chunks per row
   constexpr int KSTEPS = D / 16;             // k-steps of the score product
   constexpr int TILE_BYTES = PF_BK * D * 2;
@@ -86,9 +88,15 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, con
   if (mask_chunk > 0) first_lo = max(first_lo, pos_lo - pos_lo % mask_chunk);
   const int page_first = first_lo / PF_BK, page_last = pos_hi / PF_BK;
   // pages that hold kept first keys and lie wholly before the window's first page are walked first
-  const int n_kept_tiles = keep_first > 0 ? min(page_first, (keep_first + PF_BK - 1) / PF_BK) : 0;
+  // With pooled blocks (pool > 0): row r of the second store stands for positions r*pool .. r*pool+pool-1 and is
+  // seen from position p when r < (p - window + 1) / pool; the pages of that store that the tile's last query
+  // sees are walked first, out of their own block table, under that mask.
+  const int rows_hi = pool > 0 ? max(0, (pos_hi - window + 1) / pool) : 0;
+  const int n_kept_tiles = pool > 0 ? (rows_hi + PF_BK - 1) / PF_BK
+                                    : keep_first > 0 ? min(page_first, (keep_first + PF_BK - 1) / PF_BK) : 0;
   const int n_tiles = n_kept_tiles + page_last - page_first + 1;
   const int* pages = block_table + (size_t)b * table_width;
+  const int* pool_pages = pool > 0 ? pool_table + (size_t)b * table_width : nullptr;
   auto page_of = [&](int t) { return t < n_kept_tiles ? t : page_first + (t - n_kept_tiles); };
 
   // ---- stage the query tile -------------------------------------------------------
@@ -98,9 +106,10 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, con
     cp_async16(sQ + swz<D>(r, c), q + ((size_t)(tok0 + i0 + rr) * H + hq) * D + c * 8);
   }
   auto load_tile = [&](int t, int stage) {
-    const int phys = pages[page_of(t)];
-    const bf16* kp = k_cache + cache_row_offset(phys, g, 0, G, D);
-    const bf16* vp = v_cache + cache_row_offset(phys, g, 0, G, D);
+    const bool pooled = pool > 0 && t < n_kept_tiles;
+    const int phys = pooled ? pool_pages[t] : pages[page_of(t)];
+    const bf16* kp = (pooled ? pool_k : k_cache) + cache_row_offset(phys, g, 0, G, D);
+    const bf16* vp = (pooled ? pool_v : v_cache) + cache_row_offset(phys, g, 0, G, D);
     const uint32_t sK = sKV + stage * 2 * TILE_BYTES, sV = sK + TILE_BYTES;
     for (int idx = tid; idx < PF_BK * CHUNKS; idx += PF_THREADS) {
       const int r = idx / CHUNKS, c = idx % CHUNKS;
@@ -126,6 +135,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, con
     f0 = max(f0, p0 - p0 % mask_chunk);
     f1 = max(f1, p1 - p1 % mask_chunk);
   }
+  // how many rows of the second store this thread's two queries see
+  const int nb0 = pool > 0 ? max(0, (p0 - window + 1) / pool) : 0, nb1 = pool > 0 ? max(0, (p1 - window + 1) / pool) : 0;
 
   for (int t = 0; t < n_tiles; ++t) {
     const int stage = t & 1;
@@ -146,10 +157,12 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, con
     }
     const uint32_t sK = sKV + stage * 2 * TILE_BYTES, sV = sK + TILE_BYTES;
     const int key0 = page_of(t) * PF_BK;
-    if (key0 + PF_BK - 1 > pos_hi) {
+    const bool pooled = pool > 0 && t < n_kept_tiles;
+    const int last_row = pooled ? rows_hi - 1 : pos_hi;            // the last row of the tile's store that is seen
+    if (key0 + PF_BK - 1 > last_row) {
       // Rows of the page past the sequence's last key were never written (or belong to an earlier owner
       // of the page).  Their weights are exactly 0, but 0 * NaN is NaN, so the values are cleared.
-      const int valid = pos_hi - key0 + 1;
+      const int valid = last_row - key0 + 1;
       uint8_t* vtile = smem + (sV - sQ);
       for (int idx = tid; idx < (PF_BK - valid) * CHUNKS; idx += PF_THREADS) {
         const int r = valid + idx / CHUNKS, c = idx % CHUNKS;
@@ -184,8 +197,10 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, con
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int key = key0 + 8 * j + 2 * (lane & 3) + e;
-        s[j][e] = ((key >= f0 || key < keep_first) && key <= p0) ? s[j][e] * scale_log2 : -INFINITY;
-        s[j][2 + e] = ((key >= f1 || key < keep_first) && key <= p1) ? s[j][2 + e] * scale_log2 : -INFINITY;
+        const bool v0 = pooled ? key < nb0 : ((key >= f0 || key < keep_first) && key <= p0);
+        const bool v1 = pooled ? key < nb1 : ((key >= f1 || key < keep_first) && key <= p1);
+        s[j][e] = v0 ? s[j][e] * scale_log2 : -INFINITY;
+        s[j][2 + e] = v1 ? s[j][2 + e] * scale_log2 : -INFINITY;
         mx0 = fmaxf(mx0, s[j][e]);
         mx1 = fmaxf(mx1, s[j][2 + e]);
       }
@@ -263,8 +278,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, con
 template <int D>
 static int launch_prefill(const void* q, void* out, const void* k_cache, const void* v_cache, const int* block_table,
                           int table_width, const int* seq_start, const int* seq_past, int B, int max_new, int H,
-                          int G, int window, int keep_first, int mask_chunk, float scale, float sink,
-                          cudaStream_t stream) {
+                          int G, int window, int keep_first, int mask_chunk, float scale, float sink, int pool,
+                          const void* pool_k, const void* pool_v, const int* pool_table, cudaStream_t stream) {
   const size_t smem = (size_t)PF_BQ * D * 2 + 4 * (size_t)PF_BK * D * 2;
   auto kernel = attention_prefill_kernel<D>;
   static bool attr_set = false;
@@ -276,7 +291,8 @@ static int launch_prefill(const void* q, void* out, const void* k_cache, const v
   dim3 grid(H, (max_new + PF_BQ - 1) / PF_BQ, B);
   launch_pdl(kernel, grid, dim3(PF_THREADS), smem, stream, (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
                                              block_table, table_width, seq_start, seq_past, H, G, window,
-                                             keep_first, mask_chunk, scale * 1.4426950408889634f, sink);
+                                             keep_first, mask_chunk, scale * 1.4426950408889634f, sink, pool,
+                                             (const bf16*)pool_k, (const bf16*)pool_v, pool_table);
   return LLMX_LAUNCH_STATUS();
 }
 
@@ -285,23 +301,42 @@ static int launch_prefill(const void* q, void* out, const void* k_cache, const v
 // Head sizes 64 and 128; other sizes are refused (the general kernel takes them).
 // mask_chunk n > 0: a query sees only the keys of its own chunk of n positions, counted from the sequence's
 // position 0 (no kept first keys then).
-LLMX_API int llmx_attention_prefill_masked(const void* q, void* out, const void* k_cache, const void* v_cache,
+// pool n > 0 (beside a window, without kept first keys or a chunked mask): every block of n positions that lies
+// wholly before a query's window is seen as row b of pool_k / pool_v, a second store paged like the cache with the
+// block table pool_table (as wide as block_table).
+LLMX_API int llmx_attention_prefill_pooled(const void* q, void* out, const void* k_cache, const void* v_cache,
                                            const int* block_table, int table_width, const int* seq_start,
                                            const int* seq_past, int B, int max_new, int H, int G, int D, int window,
-                                           int keep_first, int mask_chunk, float scale, float sink,
+                                           int keep_first, int mask_chunk, float scale, float sink, int pool,
+                                           const void* pool_k, const void* pool_v, const int* pool_table,
                                            cudaStream_t stream) {
   if (B <= 0 || max_new <= 0) return 0;
+  if (pool < 0 || (pool > 0 && (window <= 0 || keep_first > 0 || mask_chunk > 0 || !pool_k || !pool_v || !pool_table ||
+                                ((uintptr_t)pool_k & 15) || ((uintptr_t)pool_v & 15))))
+    return LLMX_REFUSED(1);
   if (mask_chunk < 0 || (mask_chunk > 0 && window > 0 && keep_first > 0)) return LLMX_REFUSED(1);
   if (H <= 0 || G <= 0 || H % G || window < 0 || keep_first < 0 || B > 65535 ||
       (max_new + PF_BQ - 1) / PF_BQ > 65535)
     return LLMX_REFUSED(1);
   if (D == 128)
     return launch_prefill<128>(q, out, k_cache, v_cache, block_table, table_width, seq_start, seq_past, B, max_new,
-                               H, G, window, window > 0 ? keep_first : 0, mask_chunk, scale, sink, stream);
+                               H, G, window, window > 0 ? keep_first : 0, mask_chunk, scale, sink, pool, pool_k, pool_v,
+                               pool_table, stream);
   if (D == 64)
     return launch_prefill<64>(q, out, k_cache, v_cache, block_table, table_width, seq_start, seq_past, B, max_new, H,
-                              G, window, window > 0 ? keep_first : 0, mask_chunk, scale, sink, stream);
+                              G, window, window > 0 ? keep_first : 0, mask_chunk, scale, sink, pool, pool_k, pool_v,
+                              pool_table, stream);
   return LLMX_REFUSED(1);
+}
+
+LLMX_API int llmx_attention_prefill_masked(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                           const int* block_table, int table_width, const int* seq_start,
+                                           const int* seq_past, int B, int max_new, int H, int G, int D, int window,
+                                           int keep_first, int mask_chunk, float scale, float sink,
+                                           cudaStream_t stream) {
+  return llmx_attention_prefill_pooled(q, out, k_cache, v_cache, block_table, table_width, seq_start, seq_past, B,
+                                       max_new, H, G, D, window, keep_first, mask_chunk, scale, sink, 0, nullptr, nullptr,
+                                       nullptr, stream);
 }
 
 LLMX_API int llmx_attention_prefill(const void* q, void* out, const void* k_cache, const void* v_cache,

@@ -99,6 +99,35 @@ __global__ void latent_rope_cache_kernel(const TQ* __restrict__ q, const TQ* __r
   for (int i = lane; i < Dv; i += 32) vrow[i] = from_f32<TC>(to_f32(vp[i]));
 }
 
+// out[t, h, :] *= sigmoid(gate[t * gate_stride + h]): the heads' output gate behind an attention kernel that has none.
+template <typename TA>
+__global__ void head_gate_kernel(TA* __restrict__ out, const float* __restrict__ gate, size_t gate_stride, int H, int Dv,
+                                 size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t th = i / Dv;                             // token * H + head
+    const float z = gate[(th / H) * gate_stride + th % H];
+    out[i] = from_f32<TA>(to_f32(out[i]) * (1.0f / (1.0f + expf(-z))));
+  }
+}
+
+LLMX_API int llmx_head_gate(void* out, int dtype, const float* gate, long long gate_stride, int n_tokens, int H, int Dv,
+                            cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (H <= 0 || Dv <= 0 || gate_stride < H || !gate) return LLMX_REFUSED(1);
+  const size_t n = (size_t)n_tokens * H * Dv;
+  const size_t want = (n + 255) / 256;
+  dim3 grid((unsigned)(want < 148 * 16 ? want : 148 * 16));
+  if (dtype == LLMX_F32)
+    launch_pdl(head_gate_kernel<float>, grid, dim3(256), 0, stream, (float*)out, gate, (size_t)gate_stride, H, Dv, n);
+  else if (dtype == LLMX_BF16)
+    launch_pdl(head_gate_kernel<bf16>, grid, dim3(256), 0, stream, (bf16*)out, gate, (size_t)gate_stride, H, Dv, n);
+  else
+    return LLMX_REFUSED(2);
+  return LLMX_LAUNCH_STATUS();
+}
+
 // down: [T, row_stride] float32 or bfloat16, or n_split float32 partials split_stride elements apart.
 LLMX_API int llmx_latent_norms(const void* down, int in_dtype, int n_split, long long split_stride,
                                long long row_stride, const float* q_gain, const float* kv_gain, float eps, void* cq,

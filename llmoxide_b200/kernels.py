@@ -649,6 +649,16 @@ def latent_rope_cache(q, kv, down, k_rot_off: int, q_out, k_cache, v_cache, bloc
              ctx.n_seqs, k_cache.shape[0], _stream()), "latent_rope_cache")
 
 
+def head_gate(out, gate, n_heads: int, v_head_dim: int) -> None:
+    """out[t, h, :] *= sigmoid(gate[t, h]) in place; out [T, H*Dv], gate float32 [T, >= H] (any row stride)."""
+    _dev(out, gate)
+    _contig("out", out)
+    assert gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[1] >= n_heads
+    assert out.shape[1] == n_heads * v_head_dim and gate.shape[0] == out.shape[0]
+    f = _fn("latent_attention", "llmx_head_gate", [c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(out), _tag(out), _ptr(gate), gate.stride(0), out.shape[0], n_heads, v_head_dim, _stream()), "head_gate")
+
+
 def n_sm(device=None) -> int:
     """Streaming multiprocessors of the device (asked once)."""
     from .parts.runtime import kernels_n_sm
@@ -692,20 +702,26 @@ def _counters(device, n: int):
 
 def attention_decode(q, out, k_cache, v_cache, block_table, seq_past, n_heads: int, n_kv_heads: int,
                      head_dim: int, window, scale: float, n_chunks: int = 0, keep_first: int = 0,
-                     sink: float = 0.0, chunk: int = 0) -> None:
+                     sink: float = 0.0, chunk: int = 0, pool: int = 0, pool_k=None, pool_v=None, pool_table=None) -> None:
     """One new token per sequence, bfloat16: q, out [B,H*D] in batch order;
     seq_past[b] is the token's position.  Each sequence's keys are split over
     n_chunks CTAs (0: chosen from the batch's shape), which merge inside a
     cluster, or beyond 8 chunks through a float32 workspace.  ``chunk`` n > 0 is
-    the chunked mask of ``attention_paged`` (nothing to do with n_chunks)."""
-    _dev(q, out, k_cache, v_cache, block_table, seq_past)
+    the chunked mask of ``attention_paged`` (nothing to do with n_chunks); ``pool`` with its second store likewise."""
+    _dev(q, out, k_cache, v_cache, block_table, seq_past, pool_k, pool_v, pool_table)
     _contig("q", q), _contig("out", out), _contig("block_table", block_table)
+    if pool:
+        _contig("pool_table", pool_table)
+        assert pool_table.shape == block_table.shape and pool_k.dtype == pool_v.dtype == torch.bfloat16
+        assert pool_k.is_contiguous() and pool_v.is_contiguous() and pool_k.shape[1:] == k_cache.shape[1:]
     assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     if head_dim % 16 or head_dim > 256:
         raise Unsupported(f"head_dim {head_dim}: the decode attention kernel takes multiples of 16 up to 256")
     B = q.shape[0]
     n_pages = block_table.shape[1]
-    if window:
+    if window and pool:       # the window's pages and the pages of block rows that a full table can hold
+        n_pages = min(n_pages, (window + PAGE - 2) // PAGE + 1 + (n_pages + int(pool) - 1) // int(pool))
+    elif window:
         n_pages = min(n_pages, (window + PAGE - 2) // PAGE + 1 + (int(keep_first or 0) + PAGE - 1) // PAGE)
     if chunk:
         n_pages = min(n_pages, (int(chunk) + PAGE - 1) // PAGE + 1)
@@ -716,13 +732,15 @@ def attention_decode(q, out, k_cache, v_cache, block_table, seq_past, n_heads: i
         ws = guard.scratch((B * n_heads * n_chunks * (head_dim + 4),), torch.float32, q.device,
                            "decode attention workspace")
         counters = _counters(q.device, B * n_kv_heads * ((group + 7) // 8))
-    f = _fn("attention_decode", "llmx_attention_decode_masked",
+    f = _fn("attention_decode", "llmx_attention_decode_pooled",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p, c_void_p, c_longlong,
+             c_void_p, c_void_p])
     _check(f(_ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(block_table),
              block_table.shape[1],
              _ptr(seq_past), _ptr(ws), _ptr(counters), B, n_heads, n_kv_heads, head_dim, int(window or 0),
-             int(keep_first or 0), int(chunk or 0), scale, float(sink or 0.0), n_chunks, _stream()), "attention_decode")
+             int(keep_first or 0), int(chunk or 0), scale, float(sink or 0.0), n_chunks, int(pool or 0), _ptr(pool_k),
+             _ptr(pool_v), pool_k.shape[0] if pool else 0, _ptr(pool_table), _stream()), "attention_decode")
 
 
 def attention_decode_status() -> int:
@@ -738,20 +756,25 @@ def attention_prefill_supports(q, k_cache, head_dim: int) -> bool:
 
 def attention_prefill(q, out, k_cache, v_cache, block_table, seq_start, seq_past, n_seqs: int, max_new: int,
                       n_heads: int, n_kv_heads: int, head_dim: int, window, scale: float, keep_first: int = 0,
-                      sink: float = 0.0, chunk: int = 0) -> None:
+                      sink: float = 0.0, chunk: int = 0, pool: int = 0, pool_k=None, pool_v=None, pool_table=None) -> None:
     """Prompt attention on the tensor cores, bfloat16, head sizes 64 and 128:
     q, out [T,H*D] packed sequence after sequence.  Under a window the first ``keep_first`` keys stay visible;
-    ``chunk`` n > 0 is the chunked mask of ``attention_paged``."""
-    _dev(q, out, k_cache, v_cache, block_table, seq_start, seq_past)
+    ``chunk`` n > 0 is the chunked mask of ``attention_paged``, ``pool`` with its second store its pooled blocks."""
+    _dev(q, out, k_cache, v_cache, block_table, seq_start, seq_past, pool_k, pool_v, pool_table)
     _contig("q", q), _contig("out", out), _contig("block_table", block_table)
+    if pool:
+        _contig("pool_table", pool_table)
+        assert pool_table.shape == block_table.shape and pool_k.dtype == pool_v.dtype == torch.bfloat16
+        assert pool_k.is_contiguous() and pool_v.is_contiguous() and pool_k.shape[1:] == k_cache.shape[1:]
     if not attention_prefill_supports(q, k_cache, head_dim):
         raise Unsupported(f"the tiled prompt attention takes bfloat16 and head sizes 64 or 128, not {head_dim}")
-    f = _fn("attention_prefill", "llmx_attention_prefill_masked",
+    f = _fn("attention_prefill", "llmx_attention_prefill_pooled",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
-             c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
     _check(f(_ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
              _ptr(seq_start), _ptr(seq_past), n_seqs, max_new, n_heads, n_kv_heads, head_dim, int(window or 0),
-             int(keep_first or 0), int(chunk or 0), scale, float(sink or 0.0), _stream()), "attention_prefill")
+             int(keep_first or 0), int(chunk or 0), scale, float(sink or 0.0), int(pool or 0), _ptr(pool_k), _ptr(pool_v),
+             _ptr(pool_table), _stream()), "attention_prefill")
 
 
 def attention_prefill_tc(q, out, k_cache, v_cache, block_table, seq_start, seq_past, n_seqs: int, max_new: int,

@@ -153,11 +153,14 @@ class GQAttention:
         libs = {"elementwise"} | self.q_only.libraries() | self.o.libraries()
         if self.staged:
             libs.add("short_conv")
-        if not self.plain or self.pool:
+        if self.pool:
+            libs.add("attention")           # the blocks' means are made there
+        if not self.plain:
             return libs | {"attention"}
         if self.rt.dtype == "bfloat16" and self.rt.tensor_cores:
+            tc = self.D == 128 and not self.pool      # (pooled blocks: the mma.sync kernel, at both head sizes)
             libs |= {"attention_decode",
-                     "attention_prefill_tc" if self.D == 128 else "attention_prefill" if self.D == 64 else "attention"}
+                     "attention_prefill_tc" if tc else "attention_prefill" if self.D in (64, 128) else "attention"}
         else:
             libs.add("attention")
         return libs
@@ -222,22 +225,22 @@ class GQAttention:
         size than the keys among them) and always in float32.  All of them take
         a window that keeps its first keys, and a chunked mask."""
         H, G, D = self.H, self.G, self.D
-        fast = (self.plain and q.dtype == torch.bfloat16 and view.k.dtype == torch.bfloat16 and not self.pool
+        fast = (self.plain and q.dtype == torch.bfloat16 and view.k.dtype == torch.bfloat16
                 and self.rt.tensor_cores and self.scale > 0)       # (the tiled kernels take the maximum before the scale)
+        pooled = dict(pool=self.pool, pool_k=view.pool_k, pool_v=view.pool_v,
+                      pool_table=ctx.block_tables[view.pool_group]) if self.pool else {}
         if fast and ctx.is_decode:
             kernels.attention_decode(q, out, view.k, view.v, block_table, ctx.seq_past, H, G, D, self.window,
-                                     self.scale, keep_first=self.keep_first, sink=self.sink, chunk=self.chunk)
-        elif fast and D == 128:
+                                     self.scale, keep_first=self.keep_first, sink=self.sink, chunk=self.chunk, **pooled)
+        elif fast and D == 128 and not self.pool:
             kernels.attention_prefill_tc(q, out, view.k, view.v, block_table, ctx.seq_start, ctx.seq_past,
                                          ctx.n_seqs, ctx.max_new, H, G, D, self.window, self.scale,
                                          keep_first=self.keep_first, sink=self.sink, chunk=self.chunk)
         elif fast and kernels.attention_prefill_supports(q, view.k, D):
             kernels.attention_prefill(q, out, view.k, view.v, block_table, ctx.seq_start, ctx.seq_past,
                                       ctx.n_seqs, ctx.max_new, H, G, D, self.window, self.scale,
-                                      keep_first=self.keep_first, sink=self.sink, chunk=self.chunk)
+                                      keep_first=self.keep_first, sink=self.sink, chunk=self.chunk, **pooled)
         else:
             kernels.attention_paged(q, out, view.k, view.v, block_table, ctx.token_seq, ctx.token_pos,
                                     H, G, D, self.window, self.scale, v_head_dim=self.Dv, keep_first=self.keep_first,
-                                    sink=self.sink, chunk=self.chunk, pool=self.pool, pool_k=view.pool_k,
-                                    pool_v=view.pool_v,
-                                    pool_table=ctx.block_tables[view.pool_group] if self.pool else None)
+                                    sink=self.sink, chunk=self.chunk, **pooled)

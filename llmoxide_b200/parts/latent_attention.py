@@ -93,7 +93,7 @@ class LatentAttention:
 
     def libraries(self) -> set:
         libs = {"latent_attention", "elementwise"} | self.down.libraries() | self.uq.libraries() | self.o.libraries()
-        if self.plain and not self.gate and self.rt.dtype == "bfloat16" and self.rt.tensor_cores:
+        if self.plain and self.rt.dtype == "bfloat16" and self.rt.tensor_cores:
             libs |= {"attention_decode",
                      "attention_prefill_tc" if self.E == 128 else "attention_prefill" if self.E == 64 else "attention"}
         else:
@@ -126,7 +126,7 @@ class LatentAttention:
         head sizes 64 and 128) are followed by the gate's own small kernel."""
         H, E = self.H, self.E
         fast = (self.plain and q.dtype == torch.bfloat16 and view.k.dtype == torch.bfloat16
-                and self.rt.tensor_cores and self.scale > 0 and hasattr(kernels, "head_gate"))
+                and self.rt.tensor_cores and self.scale > 0)
         if fast and ctx.is_decode:
             kernels.attention_decode(q, out, view.k, view.v, block_table, ctx.seq_past, H, H, E, self.window, self.scale)
         elif fast and E == 128:

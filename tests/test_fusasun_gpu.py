@@ -270,6 +270,117 @@ def test_one_key_stands_out_at_every_edge_of_window_and_blocks(D, Dv, H, G, size
     kernels.check_status()
 
 
+def _pooled_case(lens, G, D, pool, seed):
+    """Random bfloat16 keys and values for sequences of the given lengths, and their store of one row per block
+    made by ``pool_blocks``; both block tables have one width."""
+    from llmoxide_b200 import kernels
+
+    g = torch.Generator().manual_seed(seed)
+    table, kc, vc = _store(lens, G, D, D, torch.bfloat16, seed)
+    ptable, pk, pv = _store([n // pool for n in lens], G, D, D, torch.bfloat16, seed + 1)
+    width = max(table.shape[1], ptable.shape[1])
+    pad = lambda t: torch.cat([t, torch.full((t.shape[0], width - t.shape[1]), -1, dtype=torch.int32)], dim=1)
+    table, ptable = pad(table), pad(ptable)
+    kc.copy_((torch.randn(kc.shape, generator=g) * 0.3).to(torch.bfloat16))
+    vc.copy_(torch.randn(vc.shape, generator=g).to(torch.bfloat16))
+    return table, kc, vc, ptable, pk, pv
+
+
+def _make_blocks(table, kc, vc, ptable, pk, pv, lens, G, D, pool):
+    from llmoxide_b200 import kernels
+
+    ctx = _ctx([0] * len(lens), lens)
+    kernels.pool_blocks(kc, vc, table.to(DEV), pk, pv, ptable.to(DEV), ctx.token_seq, ctx.token_pos, G, D, D, pool)
+
+
+@pytest.mark.parametrize("D, H, G", [(64, 8, 1), (128, 4, 2), (48, 3, 3), (96, 6, 1)])
+@pytest.mark.parametrize("size, pool", [(40, 8), (5, 8), (64, 64), (130, 16), (7, 3), (33, 1)])
+def test_decode_attention_with_pooled_blocks_equals_the_general_kernel(D, H, G, size, pool):
+    """One token per sequence at lengths around the window's, the blocks' and the pages' edges.  The key just
+    outside the window, the last block's last key or the first block's mean is made to stand out, so that a mask
+    that is one key or one block off changes the result beyond any tolerance.  Every split gives the same answer."""
+    from llmoxide_b200 import kernels
+
+    lens = [1, 2, size, size + 1, size + pool - 1, size + pool, size + pool + 1, size + 2 * pool, 64, 65, 200, 399, 129,
+            257, 64 * pool + size + 3 if pool <= 3 else 300]
+    table, kc, vc, ptable, pk, pv = _pooled_case(lens, G, D, pool, seed=D + size + pool)
+    B = len(lens)
+    q = (torch.randn(B, H, D, generator=torch.Generator().manual_seed(1)) * 0.3).to(torch.bfloat16)
+    page = kernels.PAGE
+    for b, n in enumerate(lens):
+        p = n - 1
+        nb = max(0, (p - size + 1) // pool)
+        j = [p - size, nb * pool - 1, (nb + 1) * pool - 1, 0][b % 4]
+        if 0 <= j <= p:
+            for g in range(G):
+                kc[table[b, j // page], g, j % page] = (q[b, g * (H // G)].float() * 6.0 * (pool if b % 4 else 1)).to(torch.bfloat16)
+    _make_blocks(table, kc, vc, ptable, pk, pv, lens, G, D, pool)
+    past = _i32([n - 1 for n in lens])
+    qd, td, ptd = q.view(B, H * D).to(DEV), table.to(DEV), ptable.to(DEV)
+    want = torch.empty((B, H * D), dtype=torch.bfloat16, device=DEV)
+    kernels.attention_paged(qd, want, kc, vc, td, _i32(np.arange(B)), past, H, G, D, size, 0.7, pool=pool, pool_k=pk,
+                            pool_v=pv, pool_table=ptd)
+    plain_window = torch.empty_like(want)
+    kernels.attention_paged(qd, plain_window, kc, vc, td, _i32(np.arange(B)), past, H, G, D, size, 0.7)
+    assert _rel(plain_window.float().cpu().numpy(), want.float().cpu().numpy()) > 0.1      # the blocks matter
+    for n_chunks in (0, 1, 3, 8, 11):
+        got = torch.empty_like(want)
+        kernels.attention_decode(qd, got, kc, vc, td, past, H, G, D, size, 0.7, n_chunks=n_chunks, pool=pool, pool_k=pk,
+                                 pool_v=pv, pool_table=ptd)
+        assert _rel(got.float().cpu().numpy(), want.float().cpu().numpy()) < 1.5e-2, (n_chunks,)
+    kernels.check_status()
+
+
+@pytest.mark.parametrize("D, H, G", [(64, 8, 1), (128, 4, 2)])
+@pytest.mark.parametrize("size, pool", [(40, 8), (5, 8), (64, 64), (130, 16), (7, 3), (33, 1), (200, 2)])
+def test_prompt_attention_with_pooled_blocks_equals_the_general_kernel(D, H, G, size, pool):
+    """Whole prompts and later portions (129 and 2 tokens after a cached prefix) in one launch: query tiles whose
+    queries see different numbers of blocks, none at all, and more than a page of them."""
+    from llmoxide_b200 import kernels
+
+    lens = [1, 70, 200, 399, 257, 66, 64 * pool + size + 70 if pool <= 3 else 150]
+    new = [1, 70, 200, 129, 2, 65, 100]          # the last `new` tokens of each are this step's
+    table, kc, vc, ptable, pk, pv = _pooled_case(lens, G, D, pool, seed=3 * D + size + pool)
+    T = sum(new)
+    q = (torch.randn(T, H, D, generator=torch.Generator().manual_seed(2)) * 0.3).to(torch.bfloat16)
+    start = np.concatenate([[0], np.cumsum(new)]).astype(np.int32)
+    tok_seq = np.concatenate([[b] * n for b, n in enumerate(new)]).astype(np.int32)
+    tok_pos = np.concatenate([np.arange(L - n, L) for L, n in zip(lens, new)]).astype(np.int32)
+    page = kernels.PAGE
+    for b, L in enumerate(lens):                # keys that stand out for the sequence's last query and one in the middle
+        for row, p in ((start[b + 1] - 1, L - 1), (start[b] + new[b] // 2, L - new[b] + new[b] // 2)):
+            nb = max(0, (p - size + 1) // pool)
+            j = [p - size, nb * pool - 1, (nb + 1) * pool - 1, 0][b % 4]
+            if 0 <= j <= p:
+                for g in range(G):
+                    kc[table[b, j // page], g, j % page] = (q[row, g * (H // G)].float() * 6.0 * (pool if b % 4 else 1)).to(torch.bfloat16)
+    _make_blocks(table, kc, vc, ptable, pk, pv, lens, G, D, pool)
+    qd, td, ptd = q.view(T, H * D).to(DEV), table.to(DEV), ptable.to(DEV)
+    want = torch.empty((T, H * D), dtype=torch.bfloat16, device=DEV)
+    kernels.attention_paged(qd, want, kc, vc, td, _i32(tok_seq), _i32(tok_pos), H, G, D, size, 0.7, pool=pool, pool_k=pk,
+                            pool_v=pv, pool_table=ptd)
+    past = _i32([L - n for L, n in zip(lens, new)])
+    got = torch.empty_like(want)
+    kernels.attention_prefill(qd, got, kc, vc, td, _i32(start), past, len(lens), max(new), H, G, D, size, 0.7, pool=pool,
+                              pool_k=pk, pool_v=pv, pool_table=ptd)
+    assert _rel(got.float().cpu().numpy(), want.float().cpu().numpy()) < 1.5e-2
+    kernels.check_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_output_gate_per_head(dtype):
+    from llmoxide_b200 import kernels
+
+    g = torch.Generator().manual_seed(5)
+    T, H, Dv = 37, 5, 24
+    out = torch.randn(T, H * Dv, generator=g).to(dtype)
+    wide = (torch.randn(T, 11 + H, generator=g) * 3).float()            # the gates are the last columns of wider rows
+    want = out.to(F).reshape(T, H, Dv) * torch.sigmoid(wide[:, 11:].to(F))[:, :, None]
+    dev_out, dev_wide = out.to(DEV).contiguous(), wide.to(DEV)
+    kernels.head_gate(dev_out, dev_wide[:, 11:], H, Dv)
+    assert _rel(dev_out.double().cpu().numpy(), want.reshape(T, H * Dv).numpy()) < (2e-6 if dtype == torch.float32 else 5e-3)
+
+
 # ---------------------------------------------------------------------------------------------------------
 # experts named by a table
 # ---------------------------------------------------------------------------------------------------------
