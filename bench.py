@@ -8,6 +8,7 @@ B200.  A "step" is one decode step of a batch of 8 sequences from depth 2048
     python bench.py --design tifapel    # the Tifapel decoder beside the dense decoder at equal layer sizes
     python bench.py --design voserax    # the Voserax decoder beside the Tifapel decoder's attention layers, two sizes
     python bench.py --design ninenex    # the Ninenex decoder beside the Tifapel decoder's retention and attention layers, two sizes
+    python bench.py --design fusasun    # the Fusasun decoder beside the Tifapel decoder's attention layers, two sizes
 
 ``value`` is device-timed (CUDA events around K steps queued back to back);
 ``e2e`` is the same metric through ``Session.generate`` with host token ids in
@@ -196,7 +197,7 @@ def main() -> int:
                          "one replayed decode step, when each kernel's dependency resolved")
     ap.add_argument("--cpu-baseline", action="store_true",
                     help="instead of the benchmark: time the plain implementation of tests/ on the CPU (tiny configurations)")
-    ap.add_argument("--design", choices=["tifapel", "voserax", "ninenex"], default=None,
+    ap.add_argument("--design", choices=["tifapel", "voserax", "ninenex", "fusasun"], default=None,
                     help="instead of the benchmark: prefill and decode rates of that design at layer sizes of a real "
                          "model (random weights), beside the dense Qwen3 decoder at equal sizes, with every kernel's "
                          "time per step (one JSON line of its own; the default workload is untouched)")
@@ -455,6 +456,21 @@ def ninenex_layers(n_layers, heads, kv_heads, dim, chunk, experts, top, ff):
     return out
 
 
+def fusasun_layers(n_layers, heads, kv_heads, dim, window, pool, experts, top, ff, q_rank, kv_rank):
+    """Latent attention and attention over a window with pooled blocks in turn, every layer with experts named by a
+    token table; a quarter of a latent head's query/key dimensions are rotated."""
+    moe = dict(kind="moe", expert=dict(ff=ff), router=dict(experts=experts, top=top))
+    rot = dim // 4
+    latent = dict(type="latent_attention", mlp=moe, mixer=dict(
+        heads=heads, dim=dim - rot, rot_dim=rot, vdim=dim, q_rank=q_rank, kv_rank=kv_rank, scale=dim ** -0.5,
+        mask=dict(size=window), rot=dict(dims=rot, base=500000.0,
+                                         scaling=dict(factor=4.0, original=4096, fast=32.0, slow=1.0))))
+    att = dict(type="attention", mlp=moe, mixer=dict(
+        heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, scale=dim ** -0.5, mask=dict(size=window, pool=pool),
+        rot=dict(dims=dim, base=10000.0, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192))))
+    return [json.loads(json.dumps(att if i % 2 else latent)) for i in range(n_layers)]
+
+
 def design_bench(args) -> int:
     """``--design tifapel``: prefill and decode rates of the Tifapel decoder at layer sizes that resemble a real model's (width 2048,
     16 heads of 128 on 4 key/value heads, a window of 1024 that keeps 4 tokens, 16 experts of 1024 of which a
@@ -471,7 +487,11 @@ def design_bench(args) -> int:
     ``--design ninenex``: the same measurement of the Ninenex decoder (mLSTM layers, layers with chunked attention
     beside retention, a norm before and behind every sublayer, dense feed-forwards with biases, routed experts with
     a shared expert) at the same two sizes, beside the Tifapel decoder with retention and windowed-attention layers
-    in turn (every mixer with all the heads) and routed experts."""
+    in turn (every mixer with all the heads) and routed experts.
+
+    ``--design fusasun``: the same measurement of the Fusasun decoder (latent attention and attention over a window
+    with pooled blocks in turn, a 4-tap convolution before every mixer, gated results between two norms, experts
+    named by a token table) at the same two sizes, beside the Tifapel decoder's attention layers with routed experts."""
     import numpy as np
     import torch
 
@@ -501,6 +521,27 @@ def design_bench(args) -> int:
             runs.append(dict(sizes=dict(width=width, heads=heads, kv_heads=kv, head_dim=dim, window=window, experts=E, top=top,
                                         expert_ff=ff, shared_ff=ff, streams=4, conv=4, vocab=vocab), **res))
         print(json.dumps(dict(design="voserax", unit="tokens/s", dtype="bf16", layers=L, peaks=pk_src, hbm_gbs=pk["hbm_gbs"],
+                              bf16_tflops=pk["bf16_tflops"], data="synthetic: seeded uniform token ids, random weights",
+                              runs=runs)))
+        return 0
+    if args.design == "fusasun":
+        runs = []
+        for width, heads, kv, dim, window, pool, E, top, ff, rq, rkv in ((2048, 16, 4, 128, 1024, 64, 16, 2, 1024, 512, 256),
+                                                                         (1024, 16, 8, 64, 512, 32, 8, 2, 512, 384, 128)):
+            att = dict(type="attention", mixer=dict(heads=heads, kv_heads=kv, dim=dim, vdim=dim, scale=dim ** -0.5,
+                                                    mask=dict(size=window, keep_first=0)),
+                       mlp=dict(kind="moe", expert=dict(ff=ff), router=dict(experts=E, top=top, scale=1.0)))
+            models = {
+                "fusasun": dict(architecture="Fusasun", vocab=vocab, width=width, norm=dict(eps=1e-6),
+                                embedding=dict(scale=1.0), canon=dict(taps=4),
+                                layers=fusasun_layers(L, heads, kv, dim, window, pool, E, top, ff, rq, rkv)),
+                "tifapel": dict(architecture="Tifapel", vocab=vocab, width=width, norm=dict(eps=1e-6),
+                                layers=[json.loads(json.dumps(att)) for _ in range(L)]),
+            }
+            res = _design_models(args, models, vocab, T, B, depth, rng)
+            runs.append(dict(sizes=dict(width=width, heads=heads, kv_heads=kv, head_dim=dim, window=window, pool=pool,
+                                        experts=E, top=top, expert_ff=ff, q_rank=rq, kv_rank=rkv, taps=4, vocab=vocab), **res))
+        print(json.dumps(dict(design="fusasun", unit="tokens/s", dtype="bf16", layers=L, peaks=pk_src, hbm_gbs=pk["hbm_gbs"],
                               bf16_tflops=pk["bf16_tflops"], data="synthetic: seeded uniform token ids, random weights",
                               runs=runs)))
         return 0

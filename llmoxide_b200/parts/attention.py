@@ -119,6 +119,8 @@ class GQAttention:
             self.q_gain = weights.pop(t["q_norm"].name).to(torch.float32).contiguous()
             self.k_gain = weights.pop(t["k_norm"].name).to(torch.float32).contiguous()
         self.position = position
+        if getattr(position, "pairing", "halves") == "neighbours" and ("q_norm" in t or spec.get("conv_taps")):
+            raise Unsupported("a rotation of neighbouring pairs beside a q/k norm or a short convolution is not built")
         self.taps = int(spec.get("conv_taps") or 0)
         self.sink = float(spec.get("sink") or 0.0)
         self.v_mix, self.v_mix_key = spec.get("v_mix"), spec.get("v_mix_key", "v_mix")
