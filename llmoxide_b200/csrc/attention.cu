@@ -178,7 +178,33 @@ LLMX_API int llmx_attention_paged(const void* q, void* out, int act_dtype, const
 // stored as row b of the second store.  One warp per (token, kv head); a token that ends no block does nothing.
 // The cache must still hold the block's positions: its window is at least `pool`.
 // ---------------------------------------------------------------------------
-template <typename TC>
+// One warp per (token, kv head, keys or values); a lane owns V consecutive dims (16 bytes of the cache where the
+// sizes allow it) and walks the block's positions in order with several loads in flight.
+template <int V>
+__device__ __forceinline__ void pb_load(const float* p, float* o) {
+  if (V == 1) {
+    o[0] = p[0];
+  } else {
+    const float4 x = *reinterpret_cast<const float4*>(p);
+    o[0] = x.x, o[1] = x.y, o[2] = x.z, o[3] = x.w;
+  }
+}
+template <int V>
+__device__ __forceinline__ void pb_load(const bf16* p, float* o) {
+  if (V == 1) {
+    o[0] = to_f32(p[0]);
+  } else {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __bfloat1622float2(h2[e]);
+      o[2 * e] = f.x, o[2 * e + 1] = f.y;
+    }
+  }
+}
+
+template <typename TC, int V>
 __global__ void pool_blocks_kernel(const TC* __restrict__ k_cache, const TC* __restrict__ v_cache,
                                    const int* __restrict__ block_table, TC* __restrict__ pool_k,
                                    TC* __restrict__ pool_v, const int* __restrict__ pool_table, int table_width,
@@ -186,10 +212,11 @@ __global__ void pool_blocks_kernel(const TC* __restrict__ k_cache, const TC* __r
                                    int Dv, int pool, int n_pages, int n_pool_pages) {
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int t = blockIdx.x, g = blockIdx.y * ATT_WARPS + warp;
-  if (g >= G) return;
+  const int t = blockIdx.x, unit = blockIdx.y * ATT_WARPS + warp;       // unit: kv head g's keys (2g) or values (2g+1)
+  if (unit >= 2 * G) return;
   const int p = token_pos[t];
   if ((p + 1) % pool != 0) return;
+  const int g = unit >> 1, is_v = unit & 1;
   const int b = p / pool;
   const int* pages = block_table + (size_t)token_seq[t] * table_width;
   const int dst_page = pool_table[(size_t)token_seq[t] * table_width + b / LLMX_PAGE];
@@ -197,24 +224,39 @@ __global__ void pool_blocks_kernel(const TC* __restrict__ k_cache, const TC* __r
     if (lane == 0) llmx_report(1);
     return;
   }
+  const int width = is_v ? Dv : D;
+  const TC* src = is_v ? v_cache : k_cache;
+  TC* dst = (is_v ? pool_v : pool_k) + cache_row_offset(dst_page, g, b % LLMX_PAGE, G, width);
   pdl_wait();
   const float inv = 1.0f / (float)pool;
-  for (int i = lane; i < D + Dv; i += 32) {
-    const bool is_k = i < D;
-    const int dim = is_k ? i : i - D, width = is_k ? D : Dv;
-    const TC* src = is_k ? k_cache : v_cache;
-    float sum = 0.f;
-    for (int j = p - pool + 1; j <= p; ++j) {
-      const int page = pages[j / LLMX_PAGE];
-      if (page < 0 || page >= n_pages) {
-        llmx_report(2);
-        return;
+  bool bad = false;
+  for (int d0 = lane * V; d0 < width; d0 += 32 * V) {
+    float sum[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) sum[e] = 0.f;
+    const int j0 = p - pool + 1;
+    for (int jb = 0; jb < pool; jb += 8) {                 // eight positions' loads go out together
+      float x[8][V];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int j = j0 + jb + u;
+        if (jb + u < pool) {
+          int page = pages[j / LLMX_PAGE];
+          if (page < 0 || page >= n_pages) bad = true, page = 0;
+          pb_load<V>(src + cache_row_offset(page, g, j % LLMX_PAGE, G, width) + d0, x[u]);
+        }
       }
-      sum += to_f32(src[cache_row_offset(page, g, j % LLMX_PAGE, G, width) + dim]);
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (jb + u < pool) {
+#pragma unroll
+          for (int e = 0; e < V; ++e) sum[e] += x[u][e];
+        }
     }
-    TC* dst = is_k ? pool_k : pool_v;
-    dst[cache_row_offset(dst_page, g, b % LLMX_PAGE, G, width) + dim] = from_f32<TC>(sum * inv);
+#pragma unroll
+    for (int e = 0; e < V; ++e) dst[d0 + e] = from_f32<TC>(sum[e] * inv);
   }
+  if (bad) llmx_report(2);
 }
 
 LLMX_API int llmx_pool_blocks(const void* k_cache, const void* v_cache, int cache_dtype, const int* block_table,
@@ -223,14 +265,20 @@ LLMX_API int llmx_pool_blocks(const void* k_cache, const void* v_cache, int cach
                               long long n_pool_pages, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (G <= 0 || D <= 0 || Dv <= 0 || pool < 1 || n_pages < 1 || n_pool_pages < 1) return LLMX_REFUSED(1);
-  dim3 grid(n_tokens, (G + ATT_WARPS - 1) / ATT_WARPS);
-#define CASE(TC)                                                                                              \
-  launch_pdl(pool_blocks_kernel<TC>, grid, dim3(ATT_WARPS * 32), 0, stream, (const TC*)k_cache,                \
+  dim3 grid(n_tokens, (2 * G + ATT_WARPS - 1) / ATT_WARPS);
+  const int v = cache_dtype == LLMX_BF16 ? 8 : 4;
+  const bool vec = D % v == 0 && Dv % v == 0 && !(((uintptr_t)k_cache | (uintptr_t)v_cache) & 15);
+#define CASE(TC, V)                                                                                           \
+  launch_pdl(pool_blocks_kernel<TC, V>, grid, dim3(ATT_WARPS * 32), 0, stream, (const TC*)k_cache,             \
              (const TC*)v_cache, block_table, (TC*)pool_k, (TC*)pool_v, pool_table, table_width, token_seq,    \
              token_pos, G, D, Dv, pool, (int)n_pages, (int)n_pool_pages)
-  if (cache_dtype == LLMX_F32) CASE(float);
-  else if (cache_dtype == LLMX_BF16) CASE(bf16);
-  else return LLMX_REFUSED(2);
+  if (cache_dtype == LLMX_F32) {
+    if (vec) CASE(float, 4); else CASE(float, 1);
+  } else if (cache_dtype == LLMX_BF16) {
+    if (vec) CASE(bf16, 8); else CASE(bf16, 1);
+  } else {
+    return LLMX_REFUSED(2);
+  }
 #undef CASE
   return LLMX_LAUNCH_STATUS();
 }

@@ -100,31 +100,56 @@ __global__ void latent_rope_cache_kernel(const TQ* __restrict__ q, const TQ* __r
 }
 
 // out[t, h, :] *= sigmoid(gate[t * gate_stride + h]): the heads' output gate behind an attention kernel that has none.
-template <typename TA>
+// A thread takes V consecutive values of one head (16 bytes where Dv and the address allow it).
+template <typename TA, int V>
 __global__ void head_gate_kernel(TA* __restrict__ out, const float* __restrict__ gate, size_t gate_stride, int H, int Dv,
-                                 size_t n) {
+                                 size_t n_units) {
   pdl_launch_dependents();
   pdl_wait();
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-    const size_t th = i / Dv;                             // token * H + head
+  const int per_head = Dv / V;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_units; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t th = i / per_head;                       // token * H + head
     const float z = gate[(th / H) * gate_stride + th % H];
-    out[i] = from_f32<TA>(to_f32(out[i]) * (1.0f / (1.0f + expf(-z))));
+    const float g = 1.0f / (1.0f + expf(-z));
+    TA* p = out + i * V;
+    if (V == 1) {
+      p[0] = from_f32<TA>(to_f32(p[0]) * g);
+    } else {
+      uint4 raw = *reinterpret_cast<const uint4*>(p);
+      if (sizeof(TA) == 2) {
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h2[e]);
+          h2[e] = __floats2bfloat162_rn(f.x * g, f.y * g);
+        }
+      } else {
+        float* f = reinterpret_cast<float*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) f[e] *= g;
+      }
+      *reinterpret_cast<uint4*>(p) = raw;
+    }
   }
 }
 
 LLMX_API int llmx_head_gate(void* out, int dtype, const float* gate, long long gate_stride, int n_tokens, int H, int Dv,
                             cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (H <= 0 || Dv <= 0 || gate_stride < H || !gate) return LLMX_REFUSED(1);
-  const size_t n = (size_t)n_tokens * H * Dv;
+  if (H <= 0 || Dv <= 0 || gate_stride < H || !gate || (dtype != LLMX_F32 && dtype != LLMX_BF16)) return LLMX_REFUSED(1);
+  const int v = dtype == LLMX_BF16 ? 8 : 4;
+  const bool vec = Dv % v == 0 && !((uintptr_t)out & 15);
+  const size_t n = (size_t)n_tokens * H * Dv / (vec ? v : 1);
   const size_t want = (n + 255) / 256;
   dim3 grid((unsigned)(want < 148 * 16 ? want : 148 * 16));
-  if (dtype == LLMX_F32)
-    launch_pdl(head_gate_kernel<float>, grid, dim3(256), 0, stream, (float*)out, gate, (size_t)gate_stride, H, Dv, n);
-  else if (dtype == LLMX_BF16)
-    launch_pdl(head_gate_kernel<bf16>, grid, dim3(256), 0, stream, (bf16*)out, gate, (size_t)gate_stride, H, Dv, n);
-  else
-    return LLMX_REFUSED(2);
+#define GO(TA, V) \
+  launch_pdl(head_gate_kernel<TA, V>, grid, dim3(256), 0, stream, (TA*)out, gate, (size_t)gate_stride, H, Dv, n)
+  if (dtype == LLMX_F32) {
+    if (vec) GO(float, 4); else GO(float, 1);
+  } else {
+    if (vec) GO(bf16, 8); else GO(bf16, 1);
+  }
+#undef GO
   return LLMX_LAUNCH_STATUS();
 }
 

@@ -350,7 +350,51 @@ LLMX_API int llmx_conv_state_update(const void* proj, int in_dtype, int n_split,
 // `inline_state` (every sequence brings one token) the thread, the only reader of its channel's state, moves the
 // state on itself; otherwise llmx_conv_state_update does so afterwards.
 // ---------------------------------------------------------------------------
-template <typename TX>
+// V consecutive channels per thread (one 16-byte load of x for V = 8 bfloat16 or V = 4 float32; V = 1 where the
+// width or an address does not allow it); the sums run per channel in the same order whatever V is.
+template <int V>
+__device__ __forceinline__ void rc_load(const float* p, float* o) {
+  if (V == 4) sc_load4(p, o);
+  else o[0] = p[0];
+}
+template <int V>
+__device__ __forceinline__ void rc_load(const bf16* p, float* o) {
+  if (V == 8) {
+    sc_load4(p, o);
+    sc_load4(p + 4, o + 4);
+  } else {
+    o[0] = to_f32(p[0]);
+  }
+}
+template <int V>
+__device__ __forceinline__ void rc_load_f32(const float* p, float* o) {
+  if (V == 1) {
+    o[0] = p[0];
+  } else {
+#pragma unroll
+    for (int e = 0; e < V; e += 4) sc_load4(p + e, o + e);
+  }
+}
+template <int V>
+__device__ __forceinline__ void rc_store(float* p, const float* v) {
+  if (V == 4) sc_store4(p, v);
+  else p[0] = v[0];
+}
+template <int V>
+__device__ __forceinline__ void rc_store(bf16* p, const float* v) {
+  if (V == 8) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    __nv_bfloat162 c = __floats2bfloat162_rn(v[4], v[5]), d = __floats2bfloat162_rn(v[6], v[7]);
+    uint4 raw;
+    raw.x = *reinterpret_cast<uint32_t*>(&a), raw.y = *reinterpret_cast<uint32_t*>(&b);
+    raw.z = *reinterpret_cast<uint32_t*>(&c), raw.w = *reinterpret_cast<uint32_t*>(&d);
+    *reinterpret_cast<uint4*>(p) = raw;
+  } else {
+    p[0] = from_f32<bf16>(v[0]);
+  }
+}
+
+template <typename TX, int V>
 __global__ void residual_conv_kernel(const TX* __restrict__ x, float* state, int inline_state,
                                      const float* __restrict__ conv_w, int taps, TX* __restrict__ out,
                                      const int* __restrict__ token_seq, const int* __restrict__ token_pos,
@@ -373,20 +417,33 @@ __global__ void residual_conv_kernel(const TX* __restrict__ x, float* state, int
   float* st = keep > 0 ? state + (size_t)slot * keep * C : nullptr;
   const bool move = inline_state && st && pos == p0 && seq_start[b + 1] - row0 == 1;
   pdl_wait();
-  for (size_t c = (size_t)blockIdx.y * blockDim.x + threadIdx.x; c < C; c += (size_t)gridDim.y * blockDim.x) {
-    float y = 0.f;
+  for (size_t c = ((size_t)blockIdx.y * blockDim.x + threadIdx.x) * V; c < C; c += (size_t)gridDim.y * blockDim.x * V) {
+    float y[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) y[e] = 0.f;
     for (int j = 0; j < taps; ++j) {
       const int q = pos - keep + j;                       // the position this tap reads
-      float u;
-      if (q >= p0) u = to_f32(x[(size_t)(row0 + q - p0) * C + c]);
-      else u = st[(size_t)(keep - (p0 - q)) * C + c];     // row i of the state is position p0 - keep + i
-      y += conv_w[(size_t)j * C + c] * u;
+      float u[V], w[V];
+      if (q >= p0) rc_load<V>(x + (size_t)(row0 + q - p0) * C + c, u);
+      else rc_load_f32<V>(st + (size_t)(keep - (p0 - q)) * C + c, u);     // row i of the state is position p0 - keep + i
+      rc_load_f32<V>(conv_w + (size_t)j * C + c, w);
+#pragma unroll
+      for (int e = 0; e < V; ++e) y[e] += w[e] * u[e];
     }
-    const float own = to_f32(x[(size_t)t * C + c]);
-    out[(size_t)t * C + c] = from_f32<TX>(own + y);
+    float own[V];
+    rc_load<V>(x + (size_t)t * C + c, own);
+#pragma unroll
+    for (int e = 0; e < V; ++e) y[e] = own[e] + y[e];
+    rc_store<V>(out + (size_t)t * C + c, y);
     if (move) {
-      for (int i = 0; i + 1 < keep; ++i) st[(size_t)i * C + c] = st[(size_t)(i + 1) * C + c];
-      st[(size_t)(keep - 1) * C + c] = own;
+      for (int i = 0; i + 1 < keep; ++i) {
+        float r[V];
+        rc_load_f32<V>(st + (size_t)(i + 1) * C + c, r);
+#pragma unroll
+        for (int e = 0; e < V; ++e) st[(size_t)i * C + c + e] = r[e];
+      }
+#pragma unroll
+      for (int e = 0; e < V; ++e) st[(size_t)(keep - 1) * C + c + e] = own[e];
     }
   }
 }
@@ -398,18 +455,22 @@ LLMX_API int llmx_residual_conv(const void* x, int dtype, float* state, int inli
                                 long long C, int n_seqs, int n_slots, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (C <= 0 || taps < 1 || taps > SC_MAX_TAPS || !conv_w || (taps > 1 && !state)) return LLMX_REFUSED(1);
-  const int threads = C >= 256 ? 256 : 128;
-  const long long per_row = (C + threads - 1) / threads;
+  const int v = dtype == LLMX_BF16 ? 8 : 4;
+  const bool vec = C % v == 0 && !(((uintptr_t)x | (uintptr_t)out | (uintptr_t)state | (uintptr_t)conv_w) & 15);
+  const long long units = vec ? C / v : C;              // a thread's share: v channels, or one
+  const int threads = units >= 256 ? 256 : units >= 128 ? 128 : 64;
+  const long long per_row = (units + threads - 1) / threads;
   dim3 grid(n_tokens, (unsigned)(per_row < 64 ? per_row : 64));
-  if (dtype == LLMX_F32)
-    launch_pdl(residual_conv_kernel<float>, grid, dim3(threads), 0, stream, (const float*)x, state, inline_state, conv_w,
-               taps, (float*)out, token_seq, token_pos, seq_start, seq_past, seq_slot, (size_t)C, n_tokens, n_seqs,
-               n_slots);
-  else if (dtype == LLMX_BF16)
-    launch_pdl(residual_conv_kernel<bf16>, grid, dim3(threads), 0, stream, (const bf16*)x, state, inline_state, conv_w,
-               taps, (bf16*)out, token_seq, token_pos, seq_start, seq_past, seq_slot, (size_t)C, n_tokens, n_seqs,
-               n_slots);
-  else
+#define GO(TX, V)                                                                                                       \
+  launch_pdl(residual_conv_kernel<TX, V>, grid, dim3(threads), 0, stream, (const TX*)x, state, inline_state, conv_w,    \
+             taps, (TX*)out, token_seq, token_pos, seq_start, seq_past, seq_slot, (size_t)C, n_tokens, n_seqs, n_slots)
+  if (dtype == LLMX_F32) {
+    if (vec) GO(float, 4); else GO(float, 1);
+  } else if (dtype == LLMX_BF16) {
+    if (vec) GO(bf16, 8); else GO(bf16, 1);
+  } else {
     return LLMX_REFUSED(2);
+  }
+#undef GO
   return LLMX_LAUNCH_STATUS();
 }
