@@ -49,7 +49,7 @@ FS_A = dict(
 FS_B = dict(
     architecture="Fusasun", vocab=300, width=100, norm=dict(eps=1e-6), embedding=dict(scale=0.5), canon=dict(taps=1),
     layers=[
-        _latent(5, 20, 12, 12, 36, 28, 0.3, 64, 50000.0, (2.0, 40, 8.0, 1.0), mlp=_moe(4, 4, 20)),
+        _latent(5, 20, 12, 12, 36, 28, 0.3, 64, 50000.0, (2.0, 48, 8.0, 1.0), mlp=_moe(4, 4, 20)),
         _attention(6, 3, 16, 48, 0.25, 64, 70, None, mlp=_moe(3, 1, 36)),
         _attention(3, 3, 48, 40, 0.15, 10, 3, (48, 500000.0, (2.0, 2.0, 8.0, 100)), mlp=_moe(4, 4, 20)),
     ])
@@ -60,13 +60,13 @@ FS_C = dict(
     layers=[
         _latent(2, 96, 32, 128, 64, 128, 0.09, 130, 500000.0, (2.0, 128, 32.0, 1.0), mlp=_moe(8, 2, 128)),
         _attention(4, 1, 128, 128, 0.09, 130, 16, (128, 1000000.0, (4.0, 1.0, 4.0, 256)), mlp=_moe(8, 2, 128)),
-        _attention(4, 2, 64, 64, 0.125, 40, 8, (32, 10000.0, None), mlp=_moe(8, 2, 128)),
+        _attention(8, 4, 64, 64, 0.125, 44, 12, (32, 10000.0, None), mlp=_moe(8, 2, 128)),
         _latent(4, 32, 32, 64, 96, 64, 0.125, 40, 10000.0, None, mlp=None),
     ])
 # Sizes that are no power of two, blocks of one position (every earlier key is seen), a window of two, a single
 # expert, a single head, five taps, as many key/value heads as heads.
 FS_D = dict(
-    architecture="Fusasun", vocab=1000, width=192, norm=dict(eps=1e-4), embedding=dict(scale=12.5), canon=dict(taps=5),
+    architecture="Fusasun", vocab=1000, width=184, norm=dict(eps=1e-4), embedding=dict(scale=7.5), canon=dict(taps=5),
     layers=[
         _attention(6, 2, 96, 32, 0.1, 2, 5, (32, 100.0, (16.0, 0.5, 2.0, 50)), mlp=_moe(1, 1, 72)),
         _latent(1, 40, 24, 72, 16, 200, 0.12, 300, 100000.0, (8.0, 200, 4.0, 0.5), mlp=_moe(20, 3, 72)),

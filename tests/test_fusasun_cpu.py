@@ -106,7 +106,7 @@ def test_random_table_rows_hold_different_experts(tmp_path):
 
 def test_a_group_of_one_row_per_block_holds_pages_for_complete_blocks_only():
     block = 8
-    a = CacheAllocator(3, 10, [40, None], every=[None, (block, 4)])
+    a = CacheAllocator(3, 10, [48, None], every=[None, (block, 4)])
     s = a.acquire()
     a.reserve(s, 70)
     a.commit(s, 70)
@@ -124,12 +124,12 @@ def test_a_group_of_one_row_per_block_holds_pages_for_complete_blocks_only():
     a.unreserve(s)
     assert len(a.page_row(s, 1)) == 1
     # the rows stay whatever the window gives back
-    assert a.page_row(s, 0).count(-1) == (a.length(s) - 39) // PAGE and -1 not in a.page_row(s, 1)
+    assert a.page_row(s, 0).count(-1) == (a.length(s) - 47) // PAGE and -1 not in a.page_row(s, 1)
     a.check_consistent()
     a.release(s)
     assert a.pages_held(0) == 0 and a.pages_held(1) == 0
     # its pool is its own: with one page of rows a sequence of 65 blocks does not fit, and nothing is taken
-    a = CacheAllocator(3, 10, [40, None], every=[None, (block, 1)])
+    a = CacheAllocator(3, 10, [48, None], every=[None, (block, 1)])
     s = a.acquire()
     with pytest.raises(CacheExhausted):
         a.reserve(s, (PAGE + 1) * block)
@@ -141,7 +141,7 @@ def test_a_group_of_one_row_per_block_holds_pages_for_complete_blocks_only():
 def test_cache_gives_an_entry_with_pooled_blocks_a_second_store():
     from llmoxide_b200.cache import KVNeed
 
-    need = KVNeed(2, 32, 40, v_head_dim=16, pool=8)
+    need = KVNeed(2, 32, 48, v_head_dim=16, pool=8)
     assert need.pooled() == KVNeed(2, 32, None, v_head_dim=16, every=8) and need.pooled().pool == 0
 
 
