@@ -174,12 +174,12 @@ LLMX_API int llmx_attention_paged(const void* q, void* out, int act_dtype, const
 // ---------------------------------------------------------------------------
 // The store of one row per block of `pool` positions: when a step writes the last position of block b
 // (position b*pool + pool - 1), that block's key is the mean of its `pool` keys as the cache holds them, its value
-// the mean of the values, summed in float32 from the block's first position to its last, times 1 / pool, and
-// stored as row b of the second store.  One warp per (token, kv head); a token that ends no block does nothing.
+// the mean of the values, summed in float32 in an order that `pool` alone decides, times 1 / pool, and stored as
+// row b of the second store.  A token that ends no block does nothing.
 // The cache must still hold the block's positions: its window is at least `pool`.
 // ---------------------------------------------------------------------------
-// One warp per (token, kv head, keys or values); a lane owns V consecutive dims (16 bytes of the cache where the
-// sizes allow it) and walks the block's positions in order with several loads in flight.
+// A lane owns V consecutive dims (16 bytes of the cache where the sizes allow it) and walks positions in order
+// with several loads in flight.
 template <int V>
 __device__ __forceinline__ void pb_load(const float* p, float* o) {
   if (V == 1) {
@@ -204,43 +204,48 @@ __device__ __forceinline__ void pb_load(const bf16* p, float* o) {
   }
 }
 
+#define PB_WARPS 8
+
+// One CTA per (token, kv head, keys or values).  A block's positions are cut into PB_WARPS runs of equal length; warp w
+// sums its run in position order (a lane owns V consecutive dims), and the runs' sums are added in the order of the
+// runs: an order that depends on `pool` alone.
 template <typename TC, int V>
 __global__ void pool_blocks_kernel(const TC* __restrict__ k_cache, const TC* __restrict__ v_cache,
                                    const int* __restrict__ block_table, TC* __restrict__ pool_k,
                                    TC* __restrict__ pool_v, const int* __restrict__ pool_table, int table_width,
                                    const int* __restrict__ token_seq, const int* __restrict__ token_pos, int G, int D,
                                    int Dv, int pool, int n_pages, int n_pool_pages) {
+  extern __shared__ float pb_part[];                    // [PB_WARPS][width]
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int t = blockIdx.x, unit = blockIdx.y * ATT_WARPS + warp;       // unit: kv head g's keys (2g) or values (2g+1)
-  if (unit >= 2 * G) return;
+  const int t = blockIdx.x, unit = blockIdx.y;          // unit: kv head g's keys (2g) or values (2g+1)
   const int p = token_pos[t];
-  if ((p + 1) % pool != 0) return;
+  if ((p + 1) % pool != 0) return;                      // uniform over the CTA
   const int g = unit >> 1, is_v = unit & 1;
   const int b = p / pool;
   const int* pages = block_table + (size_t)token_seq[t] * table_width;
   const int dst_page = pool_table[(size_t)token_seq[t] * table_width + b / LLMX_PAGE];
   if (dst_page < 0 || dst_page >= n_pool_pages) {
-    if (lane == 0) llmx_report(1);
+    if (threadIdx.x == 0) llmx_report(1);
     return;
   }
   const int width = is_v ? Dv : D;
   const TC* src = is_v ? v_cache : k_cache;
   TC* dst = (is_v ? pool_v : pool_k) + cache_row_offset(dst_page, g, b % LLMX_PAGE, G, width);
   pdl_wait();
-  const float inv = 1.0f / (float)pool;
+  const int run = (pool + PB_WARPS - 1) / PB_WARPS;
+  const int j_lo = p - pool + 1 + warp * run, j_hi = min(j_lo + run, p + 1);     // this warp's positions
   bool bad = false;
   for (int d0 = lane * V; d0 < width; d0 += 32 * V) {
     float sum[V];
 #pragma unroll
     for (int e = 0; e < V; ++e) sum[e] = 0.f;
-    const int j0 = p - pool + 1;
-    for (int jb = 0; jb < pool; jb += 8) {                 // eight positions' loads go out together
+    for (int jb = j_lo; jb < j_hi; jb += 8) {              // eight positions' loads go out together
       float x[8][V];
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
-        const int j = j0 + jb + u;
-        if (jb + u < pool) {
+        const int j = jb + u;
+        if (j < j_hi) {
           int page = pages[j / LLMX_PAGE];
           if (page < 0 || page >= n_pages) bad = true, page = 0;
           pb_load<V>(src + cache_row_offset(page, g, j % LLMX_PAGE, G, width) + d0, x[u]);
@@ -248,15 +253,23 @@ __global__ void pool_blocks_kernel(const TC* __restrict__ k_cache, const TC* __r
       }
 #pragma unroll
       for (int u = 0; u < 8; ++u)
-        if (jb + u < pool) {
+        if (jb + u < j_hi) {
 #pragma unroll
           for (int e = 0; e < V; ++e) sum[e] += x[u][e];
         }
     }
 #pragma unroll
-    for (int e = 0; e < V; ++e) dst[d0 + e] = from_f32<TC>(sum[e] * inv);
+    for (int e = 0; e < V; ++e) pb_part[warp * width + d0 + e] = sum[e];
   }
   if (bad) llmx_report(2);
+  __syncthreads();
+  const float inv = 1.0f / (float)pool;
+  for (int d = threadIdx.x; d < width; d += PB_WARPS * 32) {
+    float sum = pb_part[d];
+#pragma unroll
+    for (int w = 1; w < PB_WARPS; ++w) sum += pb_part[w * width + d];
+    dst[d] = from_f32<TC>(sum * inv);
+  }
 }
 
 LLMX_API int llmx_pool_blocks(const void* k_cache, const void* v_cache, int cache_dtype, const int* block_table,
@@ -265,11 +278,14 @@ LLMX_API int llmx_pool_blocks(const void* k_cache, const void* v_cache, int cach
                               long long n_pool_pages, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (G <= 0 || D <= 0 || Dv <= 0 || pool < 1 || n_pages < 1 || n_pool_pages < 1) return LLMX_REFUSED(1);
-  dim3 grid(n_tokens, (2 * G + ATT_WARPS - 1) / ATT_WARPS);
+  if (2 * G > 65535) return LLMX_REFUSED(3);
+  dim3 grid(n_tokens, 2 * G);
+  const size_t smem = (size_t)PB_WARPS * (D > Dv ? D : Dv) * sizeof(float);
+  if (smem > 48 * 1024) return LLMX_REFUSED(3);
   const int v = cache_dtype == LLMX_BF16 ? 8 : 4;
   const bool vec = D % v == 0 && Dv % v == 0 && !(((uintptr_t)k_cache | (uintptr_t)v_cache) & 15);
 #define CASE(TC, V)                                                                                           \
-  launch_pdl(pool_blocks_kernel<TC, V>, grid, dim3(ATT_WARPS * 32), 0, stream, (const TC*)k_cache,             \
+  launch_pdl(pool_blocks_kernel<TC, V>, grid, dim3(PB_WARPS * 32), smem, stream, (const TC*)k_cache,           \
              (const TC*)v_cache, block_table, (TC*)pool_k, (TC*)pool_v, pool_table, table_width, token_seq,    \
              token_pos, G, D, Dv, pool, (int)n_pages, (int)n_pool_pages)
   if (cache_dtype == LLMX_F32) {

@@ -255,7 +255,7 @@ def test_one_key_stands_out_at_every_edge_of_window_and_blocks(D, Dv, H, G, size
         if idx < 0:
             continue
         target = keys[idx] if kind == "key" else kb_c[idx]          # [G, D]
-        q = torch.stack([target[h // (H // G)] / target[h // (H // G)].pow(2).sum() for h in range(H)]) * (60.0 / 0.3)
+        q = torch.stack([target[h // (H // G)] / target[h // (H // G)].pow(2).sum() for h in range(H)]) * (300.0 / 0.3)
         q = q.to(dtype).to(F)
         got1 = attend(q.reshape(1, H * D), [p])[0]
         want1 = plain_row(q, p)
