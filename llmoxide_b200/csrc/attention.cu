@@ -175,7 +175,7 @@ LLMX_API int llmx_attention_paged(const void* q, void* out, int act_dtype, const
 // The store of one row per block of `pool` positions: when a step writes the last position of block b
 // (position b*pool + pool - 1), that block's key is the mean of its `pool` keys as the cache holds them, its value
 // the mean of the values, summed in float32 in an order that `pool` alone decides, times 1 / pool, and stored as
-// row b of the second store.  A token that ends no block does nothing.
+// row b of the second store.
 // The cache must still hold the block's positions: its window is at least `pool`.
 // ---------------------------------------------------------------------------
 // A lane owns V consecutive dims (16 bytes of the cache where the sizes allow it) and walks positions in order
@@ -206,25 +206,38 @@ __device__ __forceinline__ void pb_load(const bf16* p, float* o) {
 
 #define PB_WARPS 8
 
-// One CTA per (token, kv head, keys or values).  A block's positions are cut into PB_WARPS runs of equal length; warp w
+// One CTA per (block that ends in the step, kv head, keys or values).  A block's positions are cut into PB_WARPS runs of equal length; warp w
 // sums its run in position order (a lane owns V consecutive dims), and the runs' sums are added in the order of the
 // runs: an order that depends on `pool` alone.
 template <typename TC, int V>
 __global__ void pool_blocks_kernel(const TC* __restrict__ k_cache, const TC* __restrict__ v_cache,
                                    const int* __restrict__ block_table, TC* __restrict__ pool_k,
                                    TC* __restrict__ pool_v, const int* __restrict__ pool_table, int table_width,
-                                   const int* __restrict__ token_seq, const int* __restrict__ token_pos, int G, int D,
-                                   int Dv, int pool, int n_pages, int n_pool_pages) {
+                                   const int* __restrict__ seq_start, const int* __restrict__ seq_past, int n_seqs,
+                                   int G, int D, int Dv, int pool, int n_pages, int n_pool_pages) {
   extern __shared__ float pb_part[];                    // [PB_WARPS][width]
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int t = blockIdx.x, unit = blockIdx.y;          // unit: kv head g's keys (2g) or values (2g+1)
-  const int p = token_pos[t];
-  if ((p + 1) % pool != 0) return;                      // uniform over the CTA
+  const int unit = blockIdx.y;                          // unit: kv head g's keys (2g) or values (2g+1)
+  // The grid's x axis counts the blocks that end in this step, sequence after sequence: sequence s, which held
+  // `past` positions and brings n, ends the blocks past / pool .. (past + n) / pool - 1.  CTAs beyond the step's
+  // count leave at once (the grid is sized from the step's shape alone: tokens / pool + sequences).
+  int left = blockIdx.x, seq = -1, p = 0;
+  for (int s2 = 0; s2 < n_seqs; ++s2) {
+    const int past = seq_past[s2], n = seq_start[s2 + 1] - seq_start[s2];
+    const int first = past / pool, count = (past + n) / pool - first;
+    if (left < count) {
+      seq = s2;
+      p = (first + left) * pool + pool - 1;               // the block's last position
+      break;
+    }
+    left -= count;
+  }
+  if (seq < 0) return;                                    // uniform over the CTA
   const int g = unit >> 1, is_v = unit & 1;
   const int b = p / pool;
-  const int* pages = block_table + (size_t)token_seq[t] * table_width;
-  const int dst_page = pool_table[(size_t)token_seq[t] * table_width + b / LLMX_PAGE];
+  const int* pages = block_table + (size_t)seq * table_width;
+  const int dst_page = pool_table[(size_t)seq * table_width + b / LLMX_PAGE];
   if (dst_page < 0 || dst_page >= n_pool_pages) {
     if (threadIdx.x == 0) llmx_report(1);
     return;
@@ -272,22 +285,24 @@ __global__ void pool_blocks_kernel(const TC* __restrict__ k_cache, const TC* __r
   }
 }
 
+// seq_start [n_seqs + 1], seq_past [n_seqs]: where each sequence's tokens start in the step and how many positions it
+// held before; n_tokens: the step's tokens.
 LLMX_API int llmx_pool_blocks(const void* k_cache, const void* v_cache, int cache_dtype, const int* block_table,
-                              void* pool_k, void* pool_v, const int* pool_table, int table_width, const int* token_seq,
-                              const int* token_pos, int n_tokens, int G, int D, int Dv, int pool, long long n_pages,
-                              long long n_pool_pages, cudaStream_t stream) {
-  if (n_tokens <= 0) return 0;
+                              void* pool_k, void* pool_v, const int* pool_table, int table_width, const int* seq_start,
+                              const int* seq_past, int n_seqs, int n_tokens, int G, int D, int Dv, int pool,
+                              long long n_pages, long long n_pool_pages, cudaStream_t stream) {
+  if (n_tokens <= 0 || n_seqs <= 0) return 0;
   if (G <= 0 || D <= 0 || Dv <= 0 || pool < 1 || n_pages < 1 || n_pool_pages < 1) return LLMX_REFUSED(1);
   if (2 * G > 65535) return LLMX_REFUSED(3);
-  dim3 grid(n_tokens, 2 * G);
+  dim3 grid(n_tokens / pool + n_seqs, 2 * G);             // at least as many as blocks can end in such a step
   const size_t smem = (size_t)PB_WARPS * (D > Dv ? D : Dv) * sizeof(float);
   if (smem > 48 * 1024) return LLMX_REFUSED(3);
   const int v = cache_dtype == LLMX_BF16 ? 8 : 4;
   const bool vec = D % v == 0 && Dv % v == 0 && !(((uintptr_t)k_cache | (uintptr_t)v_cache) & 15);
 #define CASE(TC, V)                                                                                           \
   launch_pdl(pool_blocks_kernel<TC, V>, grid, dim3(PB_WARPS * 32), smem, stream, (const TC*)k_cache,           \
-             (const TC*)v_cache, block_table, (TC*)pool_k, (TC*)pool_v, pool_table, table_width, token_seq,    \
-             token_pos, G, D, Dv, pool, (int)n_pages, (int)n_pool_pages)
+             (const TC*)v_cache, block_table, (TC*)pool_k, (TC*)pool_v, pool_table, table_width, seq_start,    \
+             seq_past, n_seqs, G, D, Dv, pool, (int)n_pages, (int)n_pool_pages)
   if (cache_dtype == LLMX_F32) {
     if (vec) CASE(float, 4); else CASE(float, 1);
   } else if (cache_dtype == LLMX_BF16) {

@@ -592,19 +592,21 @@ def attention_paged(q, out, k_cache, v_cache, block_table, token_seq, token_pos,
              gate.stride(0) if gate is not None else 0, _stream()), "attention_paged")
 
 
-def pool_blocks(k_cache, v_cache, block_table, pool_k, pool_v, pool_table, token_seq, token_pos, n_kv_heads: int,
-                head_dim: int, v_head_dim: int, pool: int) -> None:
-    """For every token of the step that is the last position of a block of ``pool`` positions: the means of the
-    block's keys and values, as the cache holds them, become row ``position // pool`` of ``pool_k`` / ``pool_v``."""
-    _dev(k_cache, v_cache, block_table, pool_k, pool_v, pool_table, token_seq, token_pos)
+def pool_blocks(k_cache, v_cache, block_table, pool_k, pool_v, pool_table, seq_start, seq_past, n_seqs: int,
+                n_tokens: int, n_kv_heads: int, head_dim: int, v_head_dim: int, pool: int) -> None:
+    """For every block of ``pool`` positions whose last position the step brings (sequence s held ``seq_past[s]``
+    positions and brings ``seq_start[s+1] - seq_start[s]``): the means of the block's keys and values, as the cache
+    holds them, become row ``block`` of ``pool_k`` / ``pool_v``."""
+    _dev(k_cache, v_cache, block_table, pool_k, pool_v, pool_table, seq_start, seq_past)
     _contig("block_table", block_table), _contig("pool_table", pool_table)
     assert pool_table.shape == block_table.shape and k_cache.dtype == v_cache.dtype == pool_k.dtype == pool_v.dtype
     assert all(t.is_contiguous() for t in (k_cache, v_cache, pool_k, pool_v))
+    assert seq_start.numel() >= n_seqs + 1 and seq_past.numel() >= n_seqs
     f = _fn("attention", "llmx_pool_blocks",
             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
-             c_int, c_int, c_int, c_longlong, c_longlong, c_void_p])
+             c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p])
     _check(f(_ptr(k_cache), _ptr(v_cache), _tag(k_cache), _ptr(block_table), _ptr(pool_k), _ptr(pool_v),
-             _ptr(pool_table), block_table.shape[1], _ptr(token_seq), _ptr(token_pos), token_pos.numel(), n_kv_heads,
+             _ptr(pool_table), block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs, n_tokens, n_kv_heads,
              head_dim, v_head_dim, pool, k_cache.shape[0], pool_k.shape[0], _stream()), "pool_blocks")
 
 

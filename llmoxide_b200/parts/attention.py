@@ -212,7 +212,7 @@ class GQAttention:
                                        v_head_dim=Dv, bias=self.qkv_bias)
         if self.pool and writes_cache:
             kernels.pool_blocks(view.k, view.v, block_table, view.pool_k, view.pool_v, ctx.block_tables[view.pool_group],
-                                ctx.token_seq, ctx.token_pos, G, D, Dv, self.pool)
+                                ctx.seq_start, ctx.seq_past, ctx.n_seqs, T, G, D, Dv, self.pool)
         out = torch.empty((T, H * Dv), dtype=self.rt.act_dtype, device=dev)
         self.attend(q, out, view, block_table, ctx)
         if self.out_bias is None and residual is not None and self.o.add_into(out, residual):

@@ -208,7 +208,7 @@ def test_one_key_stands_out_at_every_edge_of_window_and_blocks(D, Dv, H, G, size
     at = 0
     for c in cuts:
         ctx = _ctx([at], [c])
-        kernels.pool_blocks(kc, vc, tab, pk, pv, ptab, ctx.token_seq, ctx.token_pos, G, D, Dv, pool)
+        kernels.pool_blocks(kc, vc, tab, pk, pv, ptab, ctx.seq_start, ctx.seq_past, ctx.n_seqs, ctx.n_tokens, G, D, Dv, pool)
         at += c
     nb = n // pool
     kb = keys[: nb * pool].reshape(nb, pool, G, D).mean(1)
@@ -290,7 +290,8 @@ def _make_blocks(table, kc, vc, ptable, pk, pv, lens, G, D, pool):
     from llmoxide_b200 import kernels
 
     ctx = _ctx([0] * len(lens), lens)
-    kernels.pool_blocks(kc, vc, table.to(DEV), pk, pv, ptable.to(DEV), ctx.token_seq, ctx.token_pos, G, D, D, pool)
+    kernels.pool_blocks(kc, vc, table.to(DEV), pk, pv, ptable.to(DEV), ctx.seq_start, ctx.seq_past, ctx.n_seqs,
+                        ctx.n_tokens, G, D, D, pool)
 
 
 @pytest.mark.parametrize("D, H, G", [(64, 8, 1), (128, 4, 2), (48, 3, 3), (96, 6, 1)])
