@@ -644,3 +644,71 @@ def test_random_weights_on_the_device_equal_the_folder(folders):
     la = a.step([(a.acquire(), toks)], [[49]])
     lb = b.step([(b.acquire(), toks)], [[49]])
     assert torch.equal(la, lb)
+
+
+def _drawn_config(rng):
+    """A configuration whose every size is drawn: odd and even head sizes, ranks and widths that are no multiple of
+    eight, windows and blocks from one position up, one to six taps, layers in any order, some without a
+    feed-forward, rotations with and without scaling."""
+    pick = lambda *xs: xs[int(rng.integers(len(xs)))]
+    width = int(pick(40, 48, 72, 100, 136, 176, 200))
+    vocab = int(rng.integers(50, 400))
+    layers = []
+    for _ in range(int(rng.integers(2, 5))):
+        E = int(rng.integers(1, 10))
+        mlp = None if rng.random() < 0.2 else dict(kind="moe", expert=dict(ff=int(pick(8, 12, 20, 24, 40, 50))),
+                                                   router=dict(experts=E, top=int(rng.integers(1, min(E, 4) + 1))))
+        if rng.random() < 0.5:
+            G = int(pick(1, 2, 3))
+            H = G * int(pick(1, 2, 3))
+            D = 2 * int(rng.integers(4, 40))
+            rot = None
+            if rng.random() < 0.85:
+                dims = 2 * int(rng.integers(1, D // 2 + 1))
+                sc = None if rng.random() < 0.3 else dict(factor=float(pick(2.0, 4.0, 8.0)), low=float(pick(0.5, 1.0)),
+                                                          high=float(pick(2.0, 4.0)), original=int(pick(16, 64, 256)))
+                rot = dict(dims=dims, base=float(pick(100.0, 10000.0, 500000.0)))
+                if sc:
+                    rot["scaling"] = sc
+            mask = dict(size=int(rng.integers(1, 90)))
+            if rng.random() < 0.85:
+                mask["pool"] = int(pick(1, 2, 3, 5, 8, 13, 20, 64, 70))
+            m = dict(heads=H, kv_heads=G, dim=D, vdim=int(rng.integers(3, 70)), scale=float(rng.uniform(0.05, 0.3)), mask=mask)
+            if rot:
+                m["rot"] = rot
+            layers.append(dict(type="attention", mixer=m, mlp=mlp))
+        else:
+            R = 2 * int(rng.integers(1, 20))
+            rot = dict(dims=R, base=float(pick(100.0, 10000.0, 500000.0)))
+            if rng.random() < 0.7:
+                rot["scaling"] = dict(factor=float(pick(2.0, 4.0, 16.0)), original=int(pick(16, 64, 512)),
+                                      fast=float(pick(8.0, 32.0)), slow=float(pick(0.5, 1.0, 2.0)))
+            layers.append(dict(type="latent_attention", mlp=mlp, mixer=dict(
+                heads=int(rng.integers(1, 7)), dim=int(rng.integers(1, 60)), rot_dim=R, vdim=int(rng.integers(3, 70)),
+                q_rank=int(rng.integers(5, 70)), kv_rank=int(rng.integers(5, 70)), scale=float(rng.uniform(0.05, 0.3)),
+                mask=dict(size=int(rng.integers(1, 90))), rot=rot)))
+    return dict(architecture="Fusasun", vocab=vocab, width=width, norm=dict(eps=float(pick(1e-5, 1e-6, 1e-3))),
+                embedding=dict(scale=float(rng.uniform(0.5, 14.0))), canon=dict(taps=int(rng.integers(1, 7))), layers=layers)
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_drawn_configurations(tmp_path, seed):
+    """Sixteen drawn configurations, each in both dtypes: whole prompts, the last 30 tokens one by one, and an
+    unequal batch, against the plain implementation."""
+    from llmoxide_b200.config import read_config
+    from llmoxide_b200.weights import write_model_folder
+
+    rng = np.random.default_rng(1000 + seed)
+    raw = _drawn_config(rng)
+    reqs = {f"r{i}": t for i, t in enumerate(prompts(raw["vocab"], [150, 37, 5, 70], seed=seed))}
+    for dtype in ("float32", "bfloat16"):
+        folder = write_model_folder(tmp_path / dtype, read_config(dict(raw, torch_dtype=dtype)), 99 + seed, dtype)
+        want = _expected(folder, reqs)
+        eng = _engine(folder, dtype, max_tokens=1024)
+        for what, steps in (("whole", ru.trace_whole(reqs)), ("last 30 one by one", ru.trace_tail_decode(reqs, 30)),
+                            ("an unequal batch", ru.trace_batches(reqs, 4, 0.4))):
+            out = tmp_path / f"{dtype}_{what.replace(' ', '_')}"
+            ru.run_in_process(eng, steps, out)
+            got = ru.collect(steps, out, raw["vocab"])
+            _compare(got, {rid: want[rid] for rid in got}, dtype, f"drawn {seed}/{dtype}/{what}: {raw}")
+        eng.check_status()
