@@ -44,6 +44,7 @@
 // the chunks are summed in chunk order, so the result does not depend on
 // timing.
 #include "tc_ptx.cuh"
+#include <type_traits>
 
 #define DEC_WARPS 2
 #define DEC_ROWS 8                           // query heads per CTA = the N of one MMA tile
@@ -114,17 +115,37 @@ struct DecSmem {
   }
 };
 
-template <int D>
+// What the kernel knows of a second store of one row per block of `pool` positions; the instance without pooled
+// blocks takes the empty form, and none of the code for them.
+struct DecPool {
+  CUtensorMap map_pk, map_pv;
+  const bf16* pool_k;
+  const bf16* pool_v;
+  const int* pool_table;
+  int pool;
+};
+struct DecNoPool {};
+
+template <int D, bool POOLED>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                         const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ seq_past,
                         float* __restrict__ ws, unsigned int* __restrict__ counters, bf16* __restrict__ out, int H,
                         int G, int window, int keep_first, int mask_chunk, float scale_log2, float sink,
-                        int n_chunks, int cluster_merge, int pool, const __grid_constant__ CUtensorMap map_pk,
-                        const __grid_constant__ CUtensorMap map_pv, const bf16* __restrict__ pool_k,
-                        const bf16* __restrict__ pool_v, const int* __restrict__ pool_table) {
+                        int n_chunks, int cluster_merge,
+                        const __grid_constant__ std::conditional_t<POOLED, DecPool, DecNoPool> pp) {
   using S = DecSmem<D>;
+  int pool = 0;
+  const CUtensorMap* map_pk = &map_k;
+  const CUtensorMap* map_pv = &map_v;
+  const bf16* pool_k = nullptr;
+  const bf16* pool_v = nullptr;
+  const int* pool_table = nullptr;
+  if constexpr (POOLED) {
+    pool = pp.pool, map_pk = &pp.map_pk, map_pv = &pp.map_pv;
+    pool_k = pp.pool_k, pool_v = pp.pool_v, pool_table = pp.pool_table;
+  }
   constexpr int KSTEPS = D / 16;
   constexpr uint32_t TILE_BYTES = 2u * DEC_TILE * D * 2u;        // what one stage's copies bring
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -167,9 +188,9 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   const int t_first = first / DEC_TILE, t_last = p / DEC_TILE;
   // With pooled blocks (pool > 0) the walk begins with the tiles of the second store instead: its row r stands
   // for positions r*pool .. r*pool+pool-1 and is seen when r < n_rows = (p - window + 1) / pool.
-  const int n_rows = pool > 0 ? max(0, (p - window + 1) / pool) : 0;
-  const int* pool_pages = pool > 0 ? pool_table + (size_t)b * table_width : nullptr;
-  const int n_kept = pool > 0 ? (n_rows + DEC_TILE - 1) / DEC_TILE
+  const int n_rows = POOLED ? max(0, (p - window + 1) / pool) : 0;
+  const int* pool_pages = POOLED ? pool_table + (size_t)b * table_width : nullptr;
+  const int n_kept = POOLED ? (n_rows + DEC_TILE - 1) / DEC_TILE
                               : keep_first > 0 ? min(t_first, (keep_first + DEC_TILE - 1) / DEC_TILE) : 0;
   const int n_walk = n_kept + t_last - t_first + 1;
   const int per_warp = (n_walk - 1 + n_chunks * DEC_WARPS) / (n_chunks * DEC_WARPS);         // ceil(tiles / warps)
@@ -182,7 +203,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   auto load_tile = [&](int place, int stage) {
     if (withhold && place == tile_lo && warp == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) return;
     const int key0 = tile_at(place) * DEC_TILE;
-    const bool pooled = pool > 0 && place < n_kept;
+    const bool pooled = POOLED && place < n_kept;
     const int phys = pooled ? pool_pages[key0 / LLMX_PAGE] : pages[key0 / LLMX_PAGE];
     const uint32_t sK = sKV + stage * 2 * S::TILE, sV = sK + S::TILE, bar = bars + 8 * stage;
     if (S::TMA) {
@@ -191,8 +212,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         mbar_expect_tx(bar, TILE_BYTES);
 #pragma unroll
         for (int pn = 0; pn < D / 64; ++pn) {
-          tma_load_2d(sK + pn * DEC_PANEL, pooled ? &map_pk : &map_k, 64 * pn, row, bar);
-          tma_load_2d(sV + pn * DEC_PANEL, pooled ? &map_pv : &map_v, 64 * pn, row, bar);
+          tma_load_2d(sK + pn * DEC_PANEL, pooled ? map_pk : &map_k, 64 * pn, row, bar);
+          tma_load_2d(sV + pn * DEC_PANEL, pooled ? map_pv : &map_v, 64 * pn, row, bar);
         }
       }
     } else {
@@ -246,7 +267,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       if (!ok) break;
       const uint32_t sK = sKV + stage * 2 * S::TILE, sV = sK + S::TILE;
       const int key0 = tile_at(tile_lo + t) * DEC_TILE;
-      const bool pooled = pool > 0 && tile_lo + t < n_kept;
+      const bool pooled = POOLED && tile_lo + t < n_kept;
       const int last_row = pooled ? n_rows - 1 : p;               // the last row of the tile's store that is seen
       if (key0 + DEC_TILE - 1 > last_row) {
         // rows past the newest key were never written by this sequence: weight 0, but 0 * NaN is NaN
@@ -525,8 +546,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   }
 }
 
-template <int D>
-static int launch_decode(const void* q, void* out, const void* k_cache, const void* v_cache, long long n_pages,
+template <int D, bool POOLED>
+static int launch_decode_as(const void* q, void* out, const void* k_cache, const void* v_cache, long long n_pages,
                          const int* block_table, int table_width, const int* seq_past, float* ws, unsigned int* counters, int B, int H, int G,
                          int window, int keep_first, int mask_chunk, float scale, float sink, int n_chunks,
                          cudaStream_t stream, int pool = 0, const void* pool_k = nullptr, const void* pool_v = nullptr,
@@ -538,7 +559,7 @@ static int launch_decode(const void* q, void* out, const void* k_cache, const vo
   size_t merge = (size_t)(DEC_WARPS + 1) * DEC_ROWS * (D + 2) * sizeof(float);
   if (merge < (size_t)DEC_ROWS * (2 * DEC_MAX_CHUNKS + 1) * sizeof(float)) merge = (size_t)DEC_ROWS * (2 * DEC_MAX_CHUNKS + 1) * sizeof(float);
   if (merge > smem) smem = merge;
-  auto kernel = attention_decode_kernel<D>;
+  auto kernel = attention_decode_kernel<D, POOLED>;
   static bool attr_set = false;
   if (!attr_set && smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -553,11 +574,15 @@ static int launch_decode(const void* q, void* out, const void* k_cache, const vo
     if (make_map(&mk, k_cache, cache_rows, D, D, DEC_TILE, false)) return LLMX_REFUSED(4);
     if (make_map(&mv, v_cache, cache_rows, D, D, DEC_TILE, false)) return LLMX_REFUSED(4);
   }
-  CUtensorMap mpk = mk, mpv = mv;        // the second store's maps (the first's again when there is none)
-  if (DecSmem<D>::TMA && pool > 0) {
-    const uint64_t pool_rows = (uint64_t)n_pool_pages * G * LLMX_PAGE;
-    if (make_map(&mpk, pool_k, pool_rows, D, D, DEC_TILE, false)) return LLMX_REFUSED(4);
-    if (make_map(&mpv, pool_v, pool_rows, D, D, DEC_TILE, false)) return LLMX_REFUSED(4);
+  std::conditional_t<POOLED, DecPool, DecNoPool> pp{};
+  if constexpr (POOLED) {
+    pp.pool = pool, pp.pool_k = (const bf16*)pool_k, pp.pool_v = (const bf16*)pool_v, pp.pool_table = pool_table;
+    pp.map_pk = mk, pp.map_pv = mv;
+    if (DecSmem<D>::TMA) {
+      const uint64_t pool_rows = (uint64_t)n_pool_pages * G * LLMX_PAGE;
+      if (make_map(&pp.map_pk, pool_k, pool_rows, D, D, DEC_TILE, false)) return LLMX_REFUSED(4);
+      if (make_map(&pp.map_pv, pool_v, pool_rows, D, D, DEC_TILE, false)) return LLMX_REFUSED(4);
+    }
   }
   // up to 8 chunks (the portable cluster size): merged inside a cluster, nothing goes through the workspace
   const int cluster_merge = (n_chunks > 1 && n_chunks <= 8) ? 1 : 0;
@@ -565,13 +590,27 @@ static int launch_decode(const void* q, void* out, const void* k_cache, const vo
     launch_pdl_cluster(kernel, grid, dim3(DEC_WARPS * 32), smem, stream, (unsigned)n_chunks, mk, mv, (const bf16*)q,
                        (const bf16*)k_cache, (const bf16*)v_cache, block_table, table_width, seq_past, ws, counters,
                        (bf16*)out, H, G, window, keep_first, mask_chunk, scale * 1.4426950408889634f, sink, n_chunks,
-                       cluster_merge, pool, mpk, mpv, (const bf16*)pool_k, (const bf16*)pool_v, pool_table);
+                       cluster_merge, pp);
   else
     launch_pdl(kernel, grid, dim3(DEC_WARPS * 32), smem, stream, mk, mv, (const bf16*)q, (const bf16*)k_cache,
                (const bf16*)v_cache, block_table, table_width, seq_past, ws, counters, (bf16*)out, H, G, window,
-               keep_first, mask_chunk, scale * 1.4426950408889634f, sink, n_chunks, cluster_merge, pool, mpk, mpv,
-               (const bf16*)pool_k, (const bf16*)pool_v, pool_table);
+               keep_first, mask_chunk, scale * 1.4426950408889634f, sink, n_chunks, cluster_merge, pp);
   return LLMX_LAUNCH_STATUS();
+}
+
+template <int D>
+static int launch_decode(const void* q, void* out, const void* k_cache, const void* v_cache, long long n_pages,
+                         const int* block_table, int table_width, const int* seq_past, float* ws, unsigned int* counters, int B, int H, int G,
+                         int window, int keep_first, int mask_chunk, float scale, float sink, int n_chunks,
+                         cudaStream_t stream, int pool = 0, const void* pool_k = nullptr, const void* pool_v = nullptr,
+                         long long n_pool_pages = 0, const int* pool_table = nullptr) {
+  if (pool > 0)
+    return launch_decode_as<D, true>(q, out, k_cache, v_cache, n_pages, block_table, table_width, seq_past, ws, counters, B,
+                                     H, G, window, keep_first, mask_chunk, scale, sink, n_chunks, stream, pool, pool_k,
+                                     pool_v, n_pool_pages, pool_table);
+  return launch_decode_as<D, false>(q, out, k_cache, v_cache, n_pages, block_table, table_width, seq_past, ws, counters, B,
+                                    H, G, window, keep_first, mask_chunk, scale, sink, n_chunks, stream, 0, nullptr,
+                                    nullptr, 0, nullptr);
 }
 
 // q, out: bf16 [B, H*D] (one token per sequence, in batch order); seq_past[b] = the token's position.

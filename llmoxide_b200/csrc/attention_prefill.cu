@@ -56,14 +56,17 @@ __device__ __forceinline__ uint32_t swz(int r, int c) {
   return (uint32_t)(r * (D * 2) + ((c ^ (r & 7)) << 4));
 }
 
-template <int D>
+// POOLED: the instance that also walks a second store of one row per block of `pool` positions; the other instance
+// carries none of that code.
+template <int D, bool POOLED>
 __global__ void __launch_bounds__(PF_THREADS)
 attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ k_cache,
                          const bf16* __restrict__ v_cache, const int* __restrict__ block_table, int table_width,
                          const int* __restrict__ seq_start, const int* __restrict__ seq_past, int H, int G,
-                         int window, int keep_first, int mask_chunk, float scale_log2, float sink, int pool,
+                         int window, int keep_first, int mask_chunk, float scale_log2, float sink, int pool_arg,
                          const bf16* __restrict__ pool_k, const bf16* __restrict__ pool_v,
                          const int* __restrict__ pool_table) {
+  const int pool = POOLED ? pool_arg : 0;
   constexpr int CHUNKS = D / 8;              // 16-byte chunks per row
   constexpr int KSTEPS = D / 16;             // k-steps of the score product
   constexpr int TILE_BYTES = PF_BK * D * 2;
@@ -91,12 +94,12 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, con
   // With pooled blocks (pool > 0): row r of the second store stands for positions r*pool .. r*pool+pool-1 and is
   // seen from position p when r < (p - window + 1) / pool; the pages of that store that the tile's last query
   // sees are walked first, out of their own block table, under that mask.
-  const int rows_hi = pool > 0 ? max(0, (pos_hi - window + 1) / pool) : 0;
-  const int n_kept_tiles = pool > 0 ? (rows_hi + PF_BK - 1) / PF_BK
+  const int rows_hi = POOLED ? max(0, (pos_hi - window + 1) / pool) : 0;
+  const int n_kept_tiles = POOLED ? (rows_hi + PF_BK - 1) / PF_BK
                                     : keep_first > 0 ? min(page_first, (keep_first + PF_BK - 1) / PF_BK) : 0;
   const int n_tiles = n_kept_tiles + page_last - page_first + 1;
   const int* pages = block_table + (size_t)b * table_width;
-  const int* pool_pages = pool > 0 ? pool_table + (size_t)b * table_width : nullptr;
+  const int* pool_pages = POOLED ? pool_table + (size_t)b * table_width : nullptr;
   auto page_of = [&](int t) { return t < n_kept_tiles ? t : page_first + (t - n_kept_tiles); };
 
   // ---- stage the query tile -------------------------------------------------------
@@ -106,7 +109,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, con
     cp_async16(sQ + swz<D>(r, c), q + ((size_t)(tok0 + i0 + rr) * H + hq) * D + c * 8);
   }
   auto load_tile = [&](int t, int stage) {
-    const bool pooled = pool > 0 && t < n_kept_tiles;
+    const bool pooled = POOLED && t < n_kept_tiles;
     const int phys = pooled ? pool_pages[t] : pages[page_of(t)];
     const bf16* kp = (pooled ? pool_k : k_cache) + cache_row_offset(phys, g, 0, G, D);
     const bf16* vp = (pooled ? pool_v : v_cache) + cache_row_offset(phys, g, 0, G, D);
@@ -136,7 +139,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, con
     f1 = max(f1, p1 - p1 % mask_chunk);
   }
   // how many rows of the second store this thread's two queries see
-  const int nb0 = pool > 0 ? max(0, (p0 - window + 1) / pool) : 0, nb1 = pool > 0 ? max(0, (p1 - window + 1) / pool) : 0;
+  const int nb0 = POOLED ? max(0, (p0 - window + 1) / pool) : 0, nb1 = POOLED ? max(0, (p1 - window + 1) / pool) : 0;
 
   for (int t = 0; t < n_tiles; ++t) {
     const int stage = t & 1;
@@ -157,7 +160,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, con
     }
     const uint32_t sK = sKV + stage * 2 * TILE_BYTES, sV = sK + TILE_BYTES;
     const int key0 = page_of(t) * PF_BK;
-    const bool pooled = pool > 0 && t < n_kept_tiles;
+    const bool pooled = POOLED && t < n_kept_tiles;
     const int last_row = pooled ? rows_hi - 1 : pos_hi;            // the last row of the tile's store that is seen
     if (key0 + PF_BK - 1 > last_row) {
       // Rows of the page past the sequence's last key were never written (or belong to an earlier owner
@@ -275,13 +278,13 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, con
   }
 }
 
-template <int D>
-static int launch_prefill(const void* q, void* out, const void* k_cache, const void* v_cache, const int* block_table,
+template <int D, bool POOLED>
+static int launch_prefill_as(const void* q, void* out, const void* k_cache, const void* v_cache, const int* block_table,
                           int table_width, const int* seq_start, const int* seq_past, int B, int max_new, int H,
                           int G, int window, int keep_first, int mask_chunk, float scale, float sink, int pool,
                           const void* pool_k, const void* pool_v, const int* pool_table, cudaStream_t stream) {
   const size_t smem = (size_t)PF_BQ * D * 2 + 4 * (size_t)PF_BK * D * 2;
-  auto kernel = attention_prefill_kernel<D>;
+  auto kernel = attention_prefill_kernel<D, POOLED>;
   static bool attr_set = false;
   if (!attr_set && smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -294,6 +297,11 @@ static int launch_prefill(const void* q, void* out, const void* k_cache, const v
                                              keep_first, mask_chunk, scale * 1.4426950408889634f, sink, pool,
                                              (const bf16*)pool_k, (const bf16*)pool_v, pool_table);
   return LLMX_LAUNCH_STATUS();
+}
+
+template <int D, typename... Args>
+static int launch_prefill(int pool, Args... args) {
+  return pool > 0 ? launch_prefill_as<D, true>(args...) : launch_prefill_as<D, false>(args...);
 }
 
 // q, out: bf16 [T, H*D], tokens packed sequence after sequence; seq_start [B+1] offsets into the packed
@@ -319,11 +327,11 @@ LLMX_API int llmx_attention_prefill_pooled(const void* q, void* out, const void*
       (max_new + PF_BQ - 1) / PF_BQ > 65535)
     return LLMX_REFUSED(1);
   if (D == 128)
-    return launch_prefill<128>(q, out, k_cache, v_cache, block_table, table_width, seq_start, seq_past, B, max_new,
+    return launch_prefill<128>(pool, q, out, k_cache, v_cache, block_table, table_width, seq_start, seq_past, B, max_new,
                                H, G, window, window > 0 ? keep_first : 0, mask_chunk, scale, sink, pool, pool_k, pool_v,
                                pool_table, stream);
   if (D == 64)
-    return launch_prefill<64>(q, out, k_cache, v_cache, block_table, table_width, seq_start, seq_past, B, max_new, H,
+    return launch_prefill<64>(pool, q, out, k_cache, v_cache, block_table, table_width, seq_start, seq_past, B, max_new, H,
                               G, window, window > 0 ? keep_first : 0, mask_chunk, scale, sink, pool, pool_k, pool_v,
                               pool_table, stream);
   return LLMX_REFUSED(1);

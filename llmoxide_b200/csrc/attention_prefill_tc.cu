@@ -60,9 +60,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
                             const int* __restrict__ block_table, int table_width, const int* __restrict__ seq_start,
                             const int* __restrict__ seq_past, int H, int G, int window, int keep_first,
-                            int mask_chunk, float scale_log2, float sink, int pool,
-                            const __grid_constant__ CUtensorMap map_pk, const __grid_constant__ CUtensorMap map_pv,
-                            const int* __restrict__ pool_table) {
+                            int mask_chunk, float scale_log2, float sink) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   pdl_launch_dependents();
   pdl_wait();
@@ -83,15 +81,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int tile_first = first_lo / AT_KEYS, tile_last = pos_hi / AT_KEYS;
   // Under a window that keeps the sequence's first keys, the tiles that hold those and lie wholly before the
   // window's first tile are walked first: place j of the walk is tile j, or past them tile_first + (j - n_kept).
-  // With pooled blocks (pool > 0) the walk begins with the pages of the second store instead: its row r stands for
-  // positions r*pool .. r*pool+pool-1 and is seen from position p when r < (p - window + 1) / pool.
-  const int rows_hi = pool > 0 ? max(0, (pos_hi - window + 1) / pool) : 0;
-  const int n_kept = pool > 0 ? (rows_hi + AT_KEYS - 1) / AT_KEYS
-                              : keep_first > 0 ? min(tile_first, (keep_first + AT_KEYS - 1) / AT_KEYS) : 0;
+  const int n_kept = keep_first > 0 ? min(tile_first, (keep_first + AT_KEYS - 1) / AT_KEYS) : 0;
   const int n_tiles = n_kept + tile_last - tile_first + 1;
   auto tile_at = [&](int j) { return j < n_kept ? j : tile_first + (j - n_kept); };
   const int* pages = block_table + (size_t)b * table_width;
-  const int* pool_pages = pool > 0 ? pool_table + (size_t)b * table_width : nullptr;
 
   // shared memory: Q (32 KB), K[2], V[2] (16 KB each), then barriers
   // Half an SM leaves no room for alignment slack: the dynamic shared memory must start on a
@@ -126,10 +119,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
-    if (pool > 0) {
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_pk) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_pv) : "memory");
-    }
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
@@ -152,19 +141,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       for (int j = 0; j < n_tiles; ++j) {
         const int st = j & 1;
         const uint32_t parity = ((j >> 1) & 1) ^ 1;
-        const bool pooled = pool > 0 && j < n_kept;
-        // the tile is one page of one kv head, of the cache or of the second store
-        const int row = ((pooled ? pool_pages : pages)[tile_at(j)] * G + g) * LLMX_PAGE;
-        const CUtensorMap* mk = pooled ? &map_pk : &map_k;
-        const CUtensorMap* mv = pooled ? &map_pv : &map_v;
+        const int row = (pages[tile_at(j)] * G + g) * LLMX_PAGE;          // the tile is one page of one kv head
         if (!mbar_wait(s_full0 + 8u * st, parity)) { at_report(1); break; }
         mbar_expect_tx(k_full0 + 8u * st, AT_KTILE);
-        tma_load_2d(sK0 + (uint32_t)st * AT_KTILE, mk, 0, row, k_full0 + 8u * st);
-        tma_load_2d(sK0 + (uint32_t)st * AT_KTILE + AT_KPANEL, mk, 64, row, k_full0 + 8u * st);
+        tma_load_2d(sK0 + (uint32_t)st * AT_KTILE, &map_k, 0, row, k_full0 + 8u * st);
+        tma_load_2d(sK0 + (uint32_t)st * AT_KTILE + AT_KPANEL, &map_k, 64, row, k_full0 + 8u * st);
         if (!mbar_wait(pv_done0 + 8u * st, parity)) { at_report(2); break; }
         mbar_expect_tx(v_full0 + 8u * st, AT_KTILE);
-        tma_load_2d(sV0 + (uint32_t)st * AT_KTILE, mv, 0, row, v_full0 + 8u * st);
-        tma_load_2d(sV0 + (uint32_t)st * AT_KTILE + AT_KPANEL, mv, 64, row, v_full0 + 8u * st);
+        tma_load_2d(sV0 + (uint32_t)st * AT_KTILE, &map_v, 0, row, v_full0 + 8u * st);
+        tma_load_2d(sV0 + (uint32_t)st * AT_KTILE + AT_KPANEL, &map_v, 64, row, v_full0 + 8u * st);
       }
     }
   } else if (warp == 1) {
@@ -212,7 +197,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     int first = (window > 0 && pos - (window - 1) > 0) ? pos - (window - 1) : 0;
     if (mask_chunk > 0) first = max(first, pos - pos % mask_chunk);
     const bool row_live = row < rows_here;
-    const int rows_seen = pool > 0 ? max(0, (pos - window + 1) / pool) : 0;   // rows of the second store this query sees
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     float m_used = -INFINITY;      // the maximum the exponentials are taken against (may lag the true one)
     float l = 0.f;                 // row sum in units of 2^-m_used
@@ -233,14 +217,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       tmem_ld_wait();
       // Tiles that some row of this CTA sees only in part (the diagonal, a window's edge, rows past the
       // sequence's end) are masked; the others, which is most of them, skip the compares.
-      const bool pooled = pool > 0 && j < n_kept;
       const bool edge = (key0 + AT_KEYS - 1 > pos_lo) || (window > 0 && key0 < pos_hi - (window - 1)) ||
                         (mask_chunk > 0 && key0 < pos_hi - pos_hi % mask_chunk) || (rows_here < AT_ROWS);
-      if (pooled) {
-#pragma unroll
-        for (int e = 0; e < AT_KEYS; ++e)
-          if (!(row_live && key0 + e < rows_seen)) sr[e] = 0xff800000u;     // -inf
-      } else if (edge) {
+      if (edge) {
 #pragma unroll
         for (int e = 0; e < AT_KEYS; ++e) {
           const int key = key0 + e;
@@ -299,13 +278,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       // P as bfloat16 over the scores it came from: this row's lane, two keys to a column
       tmem_st32_u32(tS, packed);
       // the last tile: rows of V past the newest key were never written (or belong to another owner of the page)
-      const int last_row = pooled ? rows_hi - 1 : pos_hi;         // the last row of the tile's store that anyone sees
-      if (key0 + AT_KEYS - 1 > last_row) {
+      if (key0 + AT_KEYS - 1 > pos_hi) {
         ok = mbar_wait(v_full0 + 8u * st, (j >> 1) & 1);
         if (!ok && lane == 0) at_report(9);
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (!ok) break;
-        const int valid = last_row - key0 + 1;
+        const int valid = pos_hi - key0 + 1;
         uint8_t* vt = pV0 + st * AT_KTILE;
         for (int idx = (warp - 2) * 32 + lane; idx < (AT_KEYS - valid) * 16; idx += 128) {
           const int r = valid + (idx >> 4), part = idx & 15;       // 16 x 16 bytes per row: 8 per panel
@@ -368,19 +346,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 // max_new = most new tokens of a sequence.
 // mask_chunk n > 0: a query sees only the keys of its own chunk of n positions, counted from the sequence's
 // position 0 (no kept first keys then).
-// pool n > 0 (beside a window, without kept first keys or a chunked mask): every block of n positions that lies
-// wholly before a query's window is seen as row b of pool_k / pool_v, a second store [n_pool_pages, G, 64, 128]
-// paged like the cache with the block table pool_table (as wide as block_table).
-LLMX_API int llmx_attention_prefill_tc_pooled(const void* q, void* out, const void* k_cache, const void* v_cache,
+LLMX_API int llmx_attention_prefill_tc_masked(const void* q, void* out, const void* k_cache, const void* v_cache,
                                               long long n_pages, const int* block_table, int table_width,
                                               const int* seq_start, const int* seq_past, int B, int T, int max_new,
                                               int H, int G, int D, int window, int keep_first, int mask_chunk,
-                                              float scale, float sink, int pool, const void* pool_k, const void* pool_v,
-                                              long long n_pool_pages, const int* pool_table, cudaStream_t stream) {
+                                              float scale, float sink, cudaStream_t stream) {
   if (B <= 0 || max_new <= 0 || T <= 0) return 0;
-  if (pool < 0 || (pool > 0 && (window <= 0 || keep_first > 0 || mask_chunk > 0 || !pool_k || !pool_v || !pool_table ||
-                                n_pool_pages <= 0 || ((uintptr_t)pool_k & 15) || ((uintptr_t)pool_v & 15))))
-    return LLMX_REFUSED(1);
   if (window <= 0) keep_first = 0;
   if (mask_chunk < 0 || (mask_chunk > 0 && keep_first > 0)) return LLMX_REFUSED(1);
   if (D != AT_D || H <= 0 || G <= 0 || H % G || window < 0 || keep_first < 0 || B > 65535 || (max_new + AT_ROWS - 1) / AT_ROWS > 65535 || n_pages <= 0)
@@ -391,12 +362,6 @@ LLMX_API int llmx_attention_prefill_tc_pooled(const void* q, void* out, const vo
   if (make_map(&mq, q, (uint64_t)T, (uint64_t)H * D, (uint64_t)H * D, AT_ROWS, false)) return LLMX_REFUSED(4);
   if (make_map(&mk, k_cache, cache_rows, D, D, LLMX_PAGE, false)) return LLMX_REFUSED(4);
   if (make_map(&mv, v_cache, cache_rows, D, D, LLMX_PAGE, false)) return LLMX_REFUSED(4);
-  CUtensorMap mpk = mk, mpv = mv;          // the second store's maps (the first's again when there is none)
-  if (pool > 0) {
-    const uint64_t pool_rows = (uint64_t)n_pool_pages * G * LLMX_PAGE;
-    if (make_map(&mpk, pool_k, pool_rows, D, D, LLMX_PAGE, false)) return LLMX_REFUSED(4);
-    if (make_map(&mpv, pool_v, pool_rows, D, D, LLMX_PAGE, false)) return LLMX_REFUSED(4);
-  }
   const size_t smem = AT_SMEM;
   static bool attr_set = false;
   if (!attr_set) {
@@ -411,19 +376,8 @@ LLMX_API int llmx_attention_prefill_tc_pooled(const void* q, void* out, const vo
   }
   dim3 grid(H, (max_new + AT_ROWS - 1) / AT_ROWS, B);
   launch_pdl(attention_prefill_tc_kernel, grid, dim3(AT_THREADS), smem, stream, mq, mk, mv, (bf16*)out, block_table,
-             table_width, seq_start, seq_past, H, G, window, keep_first, mask_chunk, scale * 1.4426950408889634f, sink,
-             pool, mpk, mpv, pool_table);
+             table_width, seq_start, seq_past, H, G, window, keep_first, mask_chunk, scale * 1.4426950408889634f, sink);
   return LLMX_LAUNCH_STATUS();
-}
-
-LLMX_API int llmx_attention_prefill_tc_masked(const void* q, void* out, const void* k_cache, const void* v_cache,
-                                              long long n_pages, const int* block_table, int table_width,
-                                              const int* seq_start, const int* seq_past, int B, int T, int max_new,
-                                              int H, int G, int D, int window, int keep_first, int mask_chunk,
-                                              float scale, float sink, cudaStream_t stream) {
-  return llmx_attention_prefill_tc_pooled(q, out, k_cache, v_cache, n_pages, block_table, table_width, seq_start,
-                                          seq_past, B, T, max_new, H, G, D, window, keep_first, mask_chunk, scale, sink,
-                                          0, nullptr, nullptr, 0, nullptr, stream);
 }
 
 LLMX_API int llmx_attention_prefill_tc(const void* q, void* out, const void* k_cache, const void* v_cache,

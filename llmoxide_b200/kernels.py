@@ -781,28 +781,21 @@ def attention_prefill(q, out, k_cache, v_cache, block_table, seq_start, seq_past
 
 def attention_prefill_tc(q, out, k_cache, v_cache, block_table, seq_start, seq_past, n_seqs: int, max_new: int,
                          n_heads: int, n_kv_heads: int, head_dim: int, window, scale: float, keep_first: int = 0,
-                         sink: float = 0.0, chunk: int = 0, pool: int = 0, pool_k=None, pool_v=None,
-                         pool_table=None) -> None:
+                         sink: float = 0.0, chunk: int = 0) -> None:
     """Prompt attention on tcgen05, bfloat16, head size 128: q, out [T,H*128]
     packed sequence after sequence; the cache entry is [n_pages,G,64,128].  ``chunk`` n > 0 is the chunked mask
-    of ``attention_paged``, ``pool`` with its second store its pooled blocks."""
-    _dev(q, out, k_cache, v_cache, block_table, seq_start, seq_past, pool_k, pool_v, pool_table)
+    of ``attention_paged``."""
+    _dev(q, out, k_cache, v_cache, block_table, seq_start, seq_past)
     _contig("q", q), _contig("out", out), _contig("block_table", block_table)
     assert k_cache.is_contiguous() and v_cache.is_contiguous()
-    if pool:
-        _contig("pool_table", pool_table)
-        assert pool_table.shape == block_table.shape and pool_k.dtype == pool_v.dtype == torch.bfloat16
-        assert pool_k.is_contiguous() and pool_v.is_contiguous() and pool_k.shape[1:] == k_cache.shape[1:]
     if head_dim != 128 or q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
         raise Unsupported("the tcgen05 prompt attention takes bfloat16 and head size 128")
-    f = _fn("attention_prefill_tc", "llmx_attention_prefill_tc_pooled",
+    f = _fn("attention_prefill_tc", "llmx_attention_prefill_tc_masked",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
-             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p, c_longlong,
-             c_void_p, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
     _check(f(_ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(block_table),
              block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs, q.shape[0], max_new, n_heads,
              n_kv_heads, head_dim, int(window or 0), int(keep_first or 0), int(chunk or 0), scale, float(sink or 0.0),
-             int(pool or 0), _ptr(pool_k), _ptr(pool_v), pool_k.shape[0] if pool else 0, _ptr(pool_table),
              _stream()), "attention_prefill_tc")
 
 

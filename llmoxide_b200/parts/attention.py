@@ -160,8 +160,9 @@ class GQAttention:
         if not self.plain:
             return libs | {"attention"}
         if self.rt.dtype == "bfloat16" and self.rt.tensor_cores:
+            tc = self.D == 128 and not self.pool      # (pooled blocks: the mma.sync kernel, at both head sizes)
             libs |= {"attention_decode",
-                     "attention_prefill_tc" if self.D == 128 else "attention_prefill" if self.D == 64 else "attention"}
+                     "attention_prefill_tc" if tc else "attention_prefill" if self.D in (64, 128) else "attention"}
         else:
             libs.add("attention")
         return libs
@@ -233,10 +234,10 @@ class GQAttention:
         if fast and ctx.is_decode:
             kernels.attention_decode(q, out, view.k, view.v, block_table, ctx.seq_past, H, G, D, self.window,
                                      self.scale, keep_first=self.keep_first, sink=self.sink, chunk=self.chunk, **pooled)
-        elif fast and D == 128:
+        elif fast and D == 128 and not self.pool:
             kernels.attention_prefill_tc(q, out, view.k, view.v, block_table, ctx.seq_start, ctx.seq_past,
                                          ctx.n_seqs, ctx.max_new, H, G, D, self.window, self.scale,
-                                         keep_first=self.keep_first, sink=self.sink, chunk=self.chunk, **pooled)
+                                         keep_first=self.keep_first, sink=self.sink, chunk=self.chunk)
         elif fast and kernels.attention_prefill_supports(q, view.k, D):
             kernels.attention_prefill(q, out, view.k, view.v, block_table, ctx.seq_start, ctx.seq_past,
                                       ctx.n_seqs, ctx.max_new, H, G, D, self.window, self.scale,

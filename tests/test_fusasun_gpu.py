@@ -365,11 +365,6 @@ def test_prompt_attention_with_pooled_blocks_equals_the_general_kernel(D, H, G, 
     kernels.attention_prefill(qd, got, kc, vc, td, _i32(start), past, len(lens), max(new), H, G, D, size, 0.7, pool=pool,
                               pool_k=pk, pool_v=pv, pool_table=ptd)
     assert _rel(got.float().cpu().numpy(), want.float().cpu().numpy()) < 1.5e-2
-    if D == 128:            # the tcgen05 kernel of that head size
-        got = torch.empty_like(want)
-        kernels.attention_prefill_tc(qd, got, kc, vc, td, _i32(start), past, len(lens), max(new), H, G, D, size, 0.7,
-                                     pool=pool, pool_k=pk, pool_v=pv, pool_table=ptd)
-        assert _rel(got.float().cpu().numpy(), want.float().cpu().numpy()) < 1.5e-2
     kernels.check_status()
 
 
